@@ -12,7 +12,7 @@ from . import api
 from .api import (GenerationResult, ResidentModel, generate, greedy_generate, load_resident_model,
                   random_resident_model)
 from .cache import CacheCapacityError, KVNeed, SequenceCache, StateNeed
-from .config import Qwen3Config
+from .config import LemesunConfig, Qwen3Config
 from .parts import register_part
 from .registry import register_architecture
 from .sampling import Sampler
@@ -20,5 +20,5 @@ from .weights import WeightsError, write_random_model
 
 __all__ = ["GenerationResult", "ResidentModel", "generate", "greedy_generate", "load_resident_model",
            "random_resident_model", "CacheCapacityError", "KVNeed", "SequenceCache", "StateNeed",
-           "Qwen3Config", "register_part", "register_architecture", "Sampler", "WeightsError",
+           "Qwen3Config", "LemesunConfig", "register_part", "register_architecture", "Sampler", "WeightsError",
            "write_random_model"]

@@ -86,7 +86,9 @@ def load_resident_model(model_path, *, device="cuda:0", dtype=torch.bfloat16) ->
     config = config_from_folder(model_path)
     source = SafetensorsSource(model_path)
     try:
-        decoder = DecoderModel(config.to_plan()).load(source, dtype=_dtype(dtype), device=device)
+        # a configuration may leave sizes to the checkpoint's tensor shapes: it then has plan_for(stored)
+        plan = config.plan_for(source.stored()) if hasattr(config, "plan_for") else config.to_plan()
+        decoder = DecoderModel(plan).load(source, dtype=_dtype(dtype), device=device)
     finally:
         source.close()
     return ResidentModel(config, decoder)

@@ -11,16 +11,20 @@ import torch
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values of every cached position (``window`` None) or of the last
-    ``window`` positions only."""
+    ``window`` positions only.  ``value_plane`` False: one row per position and head instead of a key row
+    and a value row (a compressed cache whose rows serve as both)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_plane: bool = True
 
 
 @dataclass(frozen=True)
 class StateNeed:
-    """A fixed-size tensor per sequence, zero when the sequence starts."""
+    """A fixed-size tensor per sequence, zero when the sequence starts.  A mixer that keeps several of
+    the same shape tells them apart by ``name``."""
 
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+    name: str = ""

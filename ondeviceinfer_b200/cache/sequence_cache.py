@@ -51,7 +51,8 @@ class KVGroup:
             # positions [p - window + 1, p + step - 1] must map to distinct rows of the ring
             self.ring_pages = pages_for(need.window + max_step_tokens - 1) + 1
         # one page and one slot beyond the capacity belong to padding rows of fixed-width steps
-        self.pool = torch.zeros((len(owners), 2, n_pages + 1, need.num_kv_heads, PAGE_SIZE, need.head_dim),
+        self.planes = 2 if need.value_plane else 1
+        self.pool = torch.zeros((len(owners), self.planes, n_pages + 1, need.num_kv_heads, PAGE_SIZE, need.head_dim),
                                 dtype=dtype, device=device)
         self.pages = IndexAllocator(n_pages, "page")
         self.pad_page = n_pages
@@ -64,8 +65,8 @@ class KVGroup:
     def keys(self, owner_pos: int) -> torch.Tensor:
         return self.pool[owner_pos, 0]
 
-    def values(self, owner_pos: int) -> torch.Tensor:
-        return self.pool[owner_pos, 1]
+    def values(self, owner_pos: int) -> Optional[torch.Tensor]:
+        return self.pool[owner_pos, 1] if self.planes == 2 else None
 
 
 class StateGroup:
@@ -82,7 +83,8 @@ class CacheView:
     keys: Optional[torch.Tensor] = None      # [pages, kv_heads, PAGE_SIZE, head_dim]
     values: Optional[torch.Tensor] = None
     writes_kv: bool = True                   # False: reads the cache another execution wrote
-    state: Optional[torch.Tensor] = None     # [slots, *shape]
+    state: Optional[torch.Tensor] = None     # [slots, *shape]: the first of `states`
+    states: Tuple[torch.Tensor, ...] = ()    # one per StateNeed of the execution's mixer, in the order it names them
 
 
 class SequenceCache:
@@ -113,6 +115,8 @@ class SequenceCache:
         for entry, entry_needs in enumerate(needs):
             if cache_from[entry] is not None:
                 continue
+            if len(set(entry_needs)) != len(entry_needs):
+                raise ValueError(f"order entry {entry} names the same cache need twice (give states a name): {entry_needs}")
             for need in entry_needs:
                 if isinstance(need, KVNeed):
                     kv_owners.setdefault(need, []).append(entry)
@@ -137,9 +141,10 @@ class SequenceCache:
                         raise ValueError(f"order entry {source} asks for two key/value stores")
                     pos = group.owners.index(source)
                     view.kv_group, view.keys, view.values = group, group.keys(pos), group.values(pos)
-            for group in self.state_groups:
-                if source in group.owners:
-                    view.state = group.data[group.owners.index(source)]
+            by_need = {group.need: group for group in self.state_groups}
+            view.states = tuple(by_need[need].data[by_need[need].owners.index(source)]
+                                for need in needs[source] if isinstance(need, StateNeed))
+            view.state = view.states[0] if view.states else None
             self._views.append(view)
 
     # ------------------------------------------------------------------ slots

@@ -22,20 +22,29 @@ def _frozen_names(names: Mapping[str, str]) -> Tuple[Tuple[str, str], ...]:
 
 @dataclass(frozen=True)
 class RMSNormSpec:
-    """y = weight * cast(x * rsqrt(mean(x^2) + eps)); statistics in fp32."""
+    """y = weight * cast(x * rsqrt(mean(x^2) + eps)); statistics in fp32.
+
+    ``weight_offset``: the row is scaled by ``weight_offset + weight`` (1.0 for a weight that is stored as its
+    deviation from one).  ``scale_in_fp32``: the scaling is done in fp32 before the one rounding to the compute
+    dtype, y = cast(x * rsqrt(mean(x^2) + eps) * (weight_offset + weight))."""
 
     size: int
     eps: float
     weight_name: str  # full checkpoint name of the [size] weight
+    weight_offset: float = 0.0
+    scale_in_fp32: bool = False
 
 
 @dataclass(frozen=True)
 class RotarySpec:
-    """Half-split rotary position encoding over the first ``rotary_dim`` lanes of a head."""
+    """Rotary position encoding over the first ``rotary_dim`` lanes of a head: lane i turns with lane
+    i + rotary_dim / 2 (half-split), or, with ``interleaved``, lane 2i with lane 2i + 1; the angle of pair i at
+    position p is p * theta^(-2i / rotary_dim)."""
 
     head_dim: int
     theta: float
     rotary_dim: Optional[int] = None  # None: the whole head
+    interleaved: bool = False
 
     @property
     def dim(self) -> int:
@@ -77,6 +86,90 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention whose keys and values are up-projections of one cached latent row per position.
+
+    Per position the cache holds the latent c (``kv_rank`` lanes: the first rows of the down projection, RMS-normed
+    with a plain weight and ``norm_eps``) and ``rot_dim`` rotated key lanes shared by all heads (the last rows of
+    the down projection).  A head's query is ``qk_dim`` plain lanes followed by ``rot_dim`` rotated lanes; its key
+    is ``W_uk c`` followed by the shared rotated lanes; its value ``W_uv c`` (``v_dim`` lanes); the score is the
+    dot product times ``scale``; ordinary softmax over positions 0..p.  ``position`` rotates the ``rot_dim`` lanes.
+    ``names`` maps the roles q, dkv, dkv_norm, uk, uv, o to tensor names below ``prefix``."""
+
+    hidden_size: int
+    num_heads: int
+    qk_dim: int
+    rot_dim: int
+    v_dim: int
+    kv_rank: int
+    scale: float
+    norm_eps: float
+    position: object
+    prefix: str
+    names: Tuple[Tuple[str, str], ...]
+
+    def name(self, role: str) -> str:
+        return self.prefix + dict(self.names)[role]
+
+
+@dataclass(frozen=True)
+class ChannelDeltaSpec:
+    """Gated delta rule with one decay per head and key channel (a recurrent mixer with a matrix state per head).
+
+    q and k have ``num_kv_heads`` heads of ``qk_dim`` lanes, v has ``num_heads`` heads of ``v_dim``; head h reads
+    q/k head h // (num_heads / num_kv_heads).  Each of q, k, v passes a causal convolution of ``conv_taps`` taps
+    per channel and SiLU; q and k become unit vectors (``unit_eps`` inside the root), q times qk_dim^-1/2.
+    Per token: S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with beta = sigmoid(b x) and
+    g = exp(-exp(A_log) softplus(a2 a1 x + dt_bias)).  o is RMS-normed per head (``norm_eps``, one plain weight of
+    ``v_dim`` lanes), gated by sigmoid(g2 g1 x), and projected by o.  ``names`` maps the roles q, k, v, q_conv,
+    k_conv, v_conv, b, A_log, dt_bias, a1, a2, g1, g2, norm, o to tensor names below ``prefix``."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    qk_dim: int
+    v_dim: int
+    conv_taps: int
+    decay_rank: int
+    gate_rank: int
+    norm_eps: float
+    prefix: str
+    names: Tuple[Tuple[str, str], ...]
+    unit_eps: float = 1e-6
+
+    def name(self, role: str) -> str:
+        return self.prefix + dict(self.names)[role]
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """Mixture of experts with a grouped top-k router, identity outputs and an optional shared expert.
+
+    The router has ``num_experts + num_identity`` outputs; scores are the softmax over all of them (fp32); the
+    choice adds ``correction`` (a stored vector, if ``has_correction``) to the scores; the outputs form
+    ``num_groups`` equal groups of neighbours of which the ``keep_groups`` with the largest member may be chosen
+    from; the ``top_k`` best are chosen and weighted by their scores (not renormalised).  The last
+    ``num_identity`` outputs pass the input on; the others are experts
+    down(g * sigmoid(``gate_alpha`` g) * (u + 1)), g = min(gate x, ``limit``), u = clamp(up x, +-``limit``).
+    ``shared_size`` > 0 adds one expert of that form (its own ``shared_limit``) for every token.
+    Tensor names below ``prefix``: ``router``, ``correction``, ``e<i>.gate|up|down``, ``shared.gate|up|down``."""
+
+    hidden_size: int
+    expert_size: int
+    num_experts: int
+    num_identity: int
+    top_k: int
+    num_groups: int
+    keep_groups: int
+    limit: float
+    prefix: str
+    has_correction: bool = True
+    shared_size: int = 0
+    shared_limit: float = 0.0
+    gate_alpha: float = 1.702
+
+
+@dataclass(frozen=True)
 class GatedMLPSpec:
     """Dense gated feed-forward: down(act(gate(x)) * up(x)), no biases."""
 
@@ -96,7 +189,7 @@ class PreNormBlockSpec:
 
     mixer_norm: object
     mixer: object
-    ffn_norm: object
+    ffn_norm: object    # None together with ffn: the layer has no feed-forward
     ffn: object
 
 

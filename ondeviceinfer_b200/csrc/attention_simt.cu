@@ -14,6 +14,11 @@
 //
 // With splits > 1 every split writes an un-normalised partial (acc[d], max, sum) and
 // attention_combine merges them in split order.
+//
+// Two more build-time options, for attention over a compressed (latent) cache:
+//  -DODI_VALUE_DIM=<dv>  the value rows (and the output) are dv wide instead of d (dv <= d when shared);
+//  -DODI_SHARED_KV=1     a cached row is key and value at once: the value is its first dv lanes, and
+//                        there is no value pool.  With these d may be any multiple of 4 up to 1024.
 #include "common.cuh"
 
 #ifndef ODI_HEAD_DIM
@@ -21,19 +26,28 @@
 #endif
 
 #define D ODI_HEAD_DIM
+#ifndef ODI_VALUE_DIM
+#define ODI_VALUE_DIM ODI_HEAD_DIM
+#endif
+#ifndef ODI_SHARED_KV
+#define ODI_SHARED_KV 0
+#endif
+#define DV ODI_VALUE_DIM
+static_assert(D % 4 == 0, "the key width must be a multiple of 4");
+static_assert(!ODI_SHARED_KV || DV <= D, "a shared row cannot hold a value wider than itself");
 #define KT 32                 // keys per tile
 #define NWARPS 4
 #define RW 4                  // rows per warp
 #define ROWS (NWARPS * RW)    // rows per block
-#define NACC ((D + 31) / 32)  // output registers per row per lane
+#define NACC ((DV + 31) / 32)  // output registers per row per lane
 #define KSTR (D + 4)          // padded row stride of the key tile (floats)
 
 struct AttnArgs {
   const void* q;        // [n_tokens, nq, D]
   const void* k_pool;   // [pages, nkv, page_size, D]
   const void* v_pool;
-  void* out;            // [n_tokens, nq * D]
-  float* partial;       // [n_tokens, nq, splits, D + 2] when splits > 1
+  void* out;            // [n_tokens, nq * DV]
+  float* partial;       // [n_tokens, nq, splits, DV + 2] when splits > 1
   const int* cu_q;      // [n_seqs + 1] first packed token of each sequence
   const int* past;      // [n_seqs] keys cached before this step
   const int* page_start;
@@ -49,8 +63,8 @@ attention_simt_kernel(AttnArgs a) {
   pdl_wait();
   extern __shared__ __align__(16) float smem[];
   float* Ks = smem;                    // [KT][KSTR]
-  float* Vs = Ks + KT * KSTR;          // [KT][D]
-  float* Qs = Vs + KT * D;             // [ROWS][D]
+  float* Vs = Ks + KT * KSTR;          // [KT][DV]; with shared rows the values are read from Ks
+  float* Qs = Vs + (ODI_SHARED_KV ? 0 : KT * DV);   // [ROWS][D]
   float* Ps = Qs + ROWS * D;           // [ROWS][KT]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -105,15 +119,16 @@ attention_simt_kernel(AttnArgs a) {
     const int page = pages[page_slot_of(kbase, a.page_size, a.ring_pages)];
     const size_t base = (((size_t)page * a.nkv + hk) * a.page_size + (kbase % a.page_size)) * D;
     const T* kp = (const T*)a.k_pool + base;
-    const T* vp = (const T*)a.v_pool + base;
     const int nkeys = min(KT, pos_hi + 1 - kbase);
     for (int i = tid; i < KT * D; i += NWARPS * 32) {
       const int j = i / D, dd = i % D;
-      float kv = 0.f, vv = 0.f;
-      if (j < nkeys) { kv = to_f<T>(kp[i]); vv = to_f<T>(vp[i]); }
-      Ks[j * KSTR + dd] = kv;
-      Vs[i] = vv;
+      Ks[j * KSTR + dd] = j < nkeys ? to_f<T>(kp[i]) : 0.f;
     }
+#if !ODI_SHARED_KV
+    const T* vp = (const T*)a.v_pool +
+                  (((size_t)page * a.nkv + hk) * a.page_size + (kbase % a.page_size)) * DV;
+    for (int i = tid; i < KT * DV; i += NWARPS * 32) Vs[i] = i / DV < nkeys ? to_f<T>(vp[i]) : 0.f;
+#endif
     __syncthreads();
 
     // scores: lane = key
@@ -159,7 +174,11 @@ attention_simt_kernel(AttnArgs a) {
 #pragma unroll
       for (int i = 0; i < NACC; ++i) {
         const int dd = lane + 32 * i;
-        vv[i] = dd < D ? Vs[j * D + dd] : 0.f;
+#if ODI_SHARED_KV
+        vv[i] = dd < DV ? Ks[j * KSTR + dd] : 0.f;
+#else
+        vv[i] = dd < DV ? Vs[j * DV + dd] : 0.f;
+#endif
       }
 #pragma unroll
       for (int r = 0; r < RW; ++r) {
@@ -179,20 +198,20 @@ attention_simt_kernel(AttnArgs a) {
     const int h = hk * g + chunk * 16 + row % hpb;
     if (a.splits == 1) {
       const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
-      T* o = (T*)a.out + ((size_t)tok * a.nq + h) * D;
+      T* o = (T*)a.out + ((size_t)tok * a.nq + h) * DV;
 #pragma unroll
       for (int i = 0; i < NACC; ++i) {
         const int dd = lane + 32 * i;
-        if (dd < D) o[dd] = from_f<T>(acc[r][i] * inv);
+        if (dd < DV) o[dd] = from_f<T>(acc[r][i] * inv);
       }
     } else {
-      float* o = a.partial + (((size_t)tok * a.nq + h) * a.splits + split) * (D + 2);
+      float* o = a.partial + (((size_t)tok * a.nq + h) * a.splits + split) * (DV + 2);
 #pragma unroll
       for (int i = 0; i < NACC; ++i) {
         const int dd = lane + 32 * i;
-        if (dd < D) o[dd] = acc[r][i];
+        if (dd < DV) o[dd] = acc[r][i];
       }
-      if (lane == 0) { o[D] = m[r]; o[D + 1] = l[r]; }
+      if (lane == 0) { o[DV] = m[r]; o[DV + 1] = l[r]; }
     }
   }
 }
@@ -203,22 +222,22 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial, T* _
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = blockIdx.x;  // token * nq + head
-  const float* p = partial + row * splits * (D + 2);
+  const float* p = partial + row * splits * (DV + 2);
   float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, p[s * (D + 2) + D]);
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, p[s * (DV + 2) + DV]);
   float denom = 0.f;
   for (int s = 0; s < splits; ++s) {
-    const float ms = p[s * (D + 2) + D];
-    if (ms != -INFINITY) denom += expf(ms - M) * p[s * (D + 2) + D + 1];
+    const float ms = p[s * (DV + 2) + DV];
+    if (ms != -INFINITY) denom += expf(ms - M) * p[s * (DV + 2) + DV + 1];
   }
   const float inv = denom > 0.f ? 1.f / denom : 0.f;
-  for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
+  for (int dd = threadIdx.x; dd < DV; dd += blockDim.x) {
     float v = 0.f;
     for (int s = 0; s < splits; ++s) {
-      const float ms = p[s * (D + 2) + D];
-      if (ms != -INFINITY) v += expf(ms - M) * p[s * (D + 2) + dd];
+      const float ms = p[s * (DV + 2) + DV];
+      if (ms != -INFINITY) v += expf(ms - M) * p[s * (DV + 2) + dd];
     }
-    out[row * D + dd] = from_f<T>(v * inv);
+    out[row * DV + dd] = from_f<T>(v * inv);
   }
 }
 
@@ -239,7 +258,7 @@ extern "C" int odi_attention_simt(const AttnArgs* args, int max_q_len, int n_tok
   const int q_tiles = (max_q_len + a.bq - 1) / a.bq;
   dim3 grid(q_tiles * a.splits, a.nkv * a.head_chunks, a.n_seqs);
   if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
-  const size_t smem = sizeof(float) * (KT * KSTR + KT * D + ROWS * D + ROWS * KT);
+  const size_t smem = sizeof(float) * (KT * KSTR + (ODI_SHARED_KV ? 0 : KT * DV) + ROWS * D + ROWS * KT);
   // The shared-memory opt-in is a property of the function, set once per process.
   static bool configured = false;
   if (!configured) {
@@ -256,7 +275,7 @@ extern "C" int odi_attention_simt(const AttnArgs* args, int max_q_len, int n_tok
   int rc = launch_status();
   if (rc != 0 || a.splits == 1) return rc;
   const int rows = n_tokens * a.nq;
-  const int threads = D >= 128 ? 128 : (D >= 64 ? 64 : 32);
+  const int threads = DV >= 128 ? 128 : (DV >= 64 ? 64 : 32);
   if (dtype == 0) odi_rc = launch_pdl((attention_combine_kernel<float>), dim3(rows), dim3(threads), 0, stream, a.partial, (float*)a.out, a.splits);
   else odi_rc = launch_pdl((attention_combine_kernel<bf16>), dim3(rows), dim3(threads), 0, stream, a.partial, (bf16*)a.out, a.splits);
   return launch_status();

@@ -491,3 +491,33 @@ extern "C" int odi_rope_table(const float* inv_freq, const int* tok_pos, float* 
   odi_rc = launch_pdl((rope_table_kernel), dim3((int)((total + 255) / 256)), dim3(256), 0, stream, inv_freq, tok_pos, cos_t, sin_t, n, half);
   return launch_status();
 }
+
+// ---------------------------------------------------------------------------------
+// RMSNorm with the scaling done in fp32: out = T(x * rsqrt(mean(x^2) + eps) * scale), one rounding.
+// `scale` is what the row is multiplied by (a norm whose stored weight is the deviation from one
+// hands in 1 + weight).  `rows` (optional) gathers input rows.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void rmsnorm_scaled_kernel(const float* __restrict__ x, const float* __restrict__ scale,
+                                      T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = xr[i]; ss += v * v; }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  T* o = out + (size_t)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f<T>(xr[i] * inv * scale[i]);
+}
+
+extern "C" int odi_rmsnorm_scaled(const float* x, const float* scale, void* out, const int* rows, int n, int H,
+                                  float eps, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  if (dtype == 0) odi_rc = launch_pdl((rmsnorm_scaled_kernel<float>), dim3(n), dim3(threads), 0, stream, x, scale, (float*)out, rows, H, eps);
+  else odi_rc = launch_pdl((rmsnorm_scaled_kernel<bf16>), dim3(n), dim3(threads), 0, stream, x, scale, (bf16*)out, rows, H, eps);
+  return launch_status();
+}

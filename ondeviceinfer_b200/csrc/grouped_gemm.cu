@@ -1,0 +1,145 @@
+// Grouped matrix product on the CUDA cores: many small products C_g = A_g W_g^T in one launch, each group with
+// a weight matrix of its own.  fp32 accumulation over k = 0..K-1 in that order for every output element,
+// whatever else is in the launch, for both element types (T = float: the true 32-bit path; T = bf16).
+//
+// Two ways to say which rows belong to which group:
+//  * dense (tile table null): every group has the same M rows; group g reads columns [g * a_group_off, +K) of
+//    A's rows 0..M-1 and writes columns [g * c_group_off, +N) of C's rows (a product per head);
+//  * by table (routed experts): tile t covers `tile_rows[t]` rows from `tile_row0[t]` on, in an order sorted
+//    by group, all of group `tile_group[t]`; `n_tiles[0]` tiles exist (blocks beyond it leave).  Row i of that
+//    order reads row `row_index[i] / index_div` of A (row i itself if row_index is null) and writes row i of C.
+//
+// Epilogues: 0 store as T, 1 store as fp32, 2 gated and clamped (W_g holds N gate rows then N up rows;
+// g = min(gate, limit), u = clamp(up, -limit, limit), C = g * sigmoid(alpha * g) * (u + 1) as T).
+//
+// Tile: TM rows x 64 features per block of 256 threads, K in slices of 16 through shared memory (fp32).
+// TM = 64 (4 x 4 outputs a thread) or 16 (1 x 4), chosen by the caller from the rows a group has.
+#include "common.cuh"
+
+#define TN 64
+#define TK 16
+
+struct GroupedArgs {
+  const void* A;
+  const void* W;
+  void* C;
+  const int* row_index;
+  const int* tile_group;
+  const int* tile_row0;
+  const int* tile_rows;
+  const int* n_tiles;
+  long long a_group_off, w_group_stride, c_group_off;
+  int lda, ldw, ldc, M, N, K, groups, index_div, epi;
+  float limit, alpha;
+};
+
+template <typename T, int TM, bool GATED>
+__global__ void __launch_bounds__(256)
+grouped_gemm_kernel(GroupedArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int RPT = TM / 16;
+  __shared__ __align__(16) float As[TK][TM + 4];
+  __shared__ __align__(16) float Ws[GATED ? 2 : 1][TK][TN + 4];
+  __shared__ int arow[TM];
+  const int tid = threadIdx.x;
+  int group, row0, rows;
+  if (a.tile_group != nullptr) {
+    const int t = blockIdx.x;
+    if (t >= a.n_tiles[0]) return;
+    group = a.tile_group[t]; row0 = a.tile_row0[t]; rows = a.tile_rows[t];
+  } else {
+    group = blockIdx.z; row0 = blockIdx.x * TM; rows = min(TM, a.M - row0);
+  }
+  const int n0 = blockIdx.y * TN;
+  if (tid < TM) {
+    int r = -1;
+    if (tid < rows) r = a.row_index != nullptr ? a.row_index[row0 + tid] / a.index_div : row0 + tid;
+    arow[tid] = r;
+  }
+  __syncthreads();
+  const T* A = (const T*)a.A + (a.tile_group != nullptr ? 0 : (size_t)group * a.a_group_off);
+  const T* W = (const T*)a.W + (size_t)group * a.w_group_stride;
+  const int tx = tid & 15, ty = tid >> 4;
+  float acc[GATED ? 2 : 1][RPT][4] = {};
+
+  for (int k0 = 0; k0 < a.K; k0 += TK) {
+    __syncthreads();
+    for (int i = tid; i < TM * TK; i += 256) {
+      const int r = i / TK, k = i % TK;
+      const int src = arow[r];
+      As[k][r] = (src >= 0 && k0 + k < a.K) ? to_f<T>(A[(size_t)src * a.lda + k0 + k]) : 0.f;
+    }
+    for (int i = tid; i < TN * TK; i += 256) {
+      const int n = i / TK, k = i % TK;
+      const bool in = n0 + n < a.N && k0 + k < a.K;
+      Ws[0][k][n] = in ? to_f<T>(W[(size_t)(n0 + n) * a.ldw + k0 + k]) : 0.f;
+      if (GATED) Ws[1][k][n] = in ? to_f<T>(W[(size_t)(a.N + n0 + n) * a.ldw + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < TK; ++k) {
+      float ar[RPT];
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) ar[i] = As[k][ty * RPT + i];
+#pragma unroll
+      for (int s = 0; s < (GATED ? 2 : 1); ++s) {
+        const float4 wv = *(const float4*)&Ws[s][k][tx * 4];
+        const float wr[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int i = 0; i < RPT; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[s][i][j] = fmaf(ar[i], wr[j], acc[s][i][j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int r = ty * RPT + i;
+    if (r >= rows) continue;
+    const size_t crow = (size_t)(row0 + r) * a.ldc + (a.tile_group != nullptr ? 0 : (size_t)group * a.c_group_off);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= a.N) continue;
+      if (GATED) {
+        const float g = fminf(acc[0][i][j], a.limit);
+        const float u = fminf(fmaxf(acc[GATED ? 1 : 0][i][j], -a.limit), a.limit);
+        ((T*)a.C)[crow + n] = from_f<T>(g / (1.f + expf(-a.alpha * g)) * (u + 1.f));
+      } else if (a.epi == 1) {
+        ((float*)a.C)[crow + n] = acc[0][i][j];
+      } else {
+        ((T*)a.C)[crow + n] = from_f<T>(acc[0][i][j]);
+      }
+    }
+  }
+}
+
+// max_tiles: with a tile table, the most tiles the table can hold (the grid's width); tm: 16 or 64 (the
+// table must have been built for the same tm).
+extern "C" int odi_grouped_gemm(const GroupedArgs* args, int max_tiles, int tm, int dtype, cudaStream_t stream) {
+  const GroupedArgs a = *args;
+  if (a.N <= 0 || a.groups <= 0) return 0;
+  if (a.K <= 0 || (tm != 16 && tm != 64) || a.epi < 0 || a.epi > 2) return ODI_ERR_ARGUMENT;
+  dim3 grid;
+  if (a.tile_group != nullptr) {
+    if (max_tiles <= 0) return 0;
+    grid = dim3(max_tiles, (a.N + TN - 1) / TN, 1);
+  } else {
+    if (a.M <= 0) return 0;
+    grid = dim3((a.M + tm - 1) / tm, (a.N + TN - 1) / TN, a.groups);
+    if (grid.z > 65535) return ODI_ERR_UNSUPPORTED;
+  }
+  if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
+#define ODI_GG(T, TM, G) odi_rc = launch_pdl((grouped_gemm_kernel<T, TM, G>), grid, dim3(256), 0, stream, a)
+  const bool gated = a.epi == 2;
+  if (dtype == 0) {
+    if (tm == 64) { if (gated) ODI_GG(float, 64, true); else ODI_GG(float, 64, false); }
+    else { if (gated) ODI_GG(float, 16, true); else ODI_GG(float, 16, false); }
+  } else {
+    if (tm == 64) { if (gated) ODI_GG(bf16, 64, true); else ODI_GG(bf16, 64, false); }
+    else { if (gated) ODI_GG(bf16, 16, true); else ODI_GG(bf16, 16, false); }
+  }
+#undef ODI_GG
+  return launch_status();
+}

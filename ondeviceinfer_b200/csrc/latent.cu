@@ -1,0 +1,89 @@
+// Head preparation of latent attention: what lies between the fused query / down projection and the
+// attention kernel over the compressed cache.
+//
+// One block per token reads its row of the projection output
+//   [ head 0: d plain lanes, r rotated lanes | head 1 ... | R latent lanes | r shared rotated key lanes ]
+// and
+//  * norms the R latent lanes (RMS over R in fp32, times a plain weight, eps inside the root), rounds them
+//    once to T and writes them to lanes 0..R-1 of the token's row in the paged cache;
+//  * rotates the shared key lanes and writes them to lanes R..R+r-1 of that row;
+//  * rotates each head's r query lanes and writes them to lanes R..R+r-1 of that head's row of the
+//    absorbed query [tokens, heads, R + r] (lanes 0..R-1 are left to the product that folds the key
+//    up-projection into the query).
+// Rotation: lanes (2i, 2i+1), i < rot_dims / 2, turn by the angle whose cosine and sine the step's
+// tables hold (fp32); lanes from rot_dims on pass unchanged.  `interleaved == 0` pairs lane i with lane
+// i + rot_dims / 2 instead.
+#include "common.cuh"
+
+struct LatentPrepArgs {
+  const void* proj;      // [n_tokens, ld] in T
+  void* q_abs;           // [n_tokens, heads, R + r] in T
+  void* pool;            // [pages, 1, page_size, R + r] in T
+  const float* norm_w;   // [R]
+  const float* cos_t;    // [n_tokens, rot_dims / 2]
+  const float* sin_t;
+  const int* tok_seq;
+  const int* tok_pos;
+  const int* page_start;
+  const int* page_ids;
+  int n_tokens, ld, heads, d, r, R, rot_dims, interleaved, page_size, ring_pages, write_cache;
+  float eps;
+};
+
+__device__ __forceinline__ void rotated_pair(int lane, int rot_dims, int interleaved, int* a, int* b, int* i) {
+  // the pair that `lane` belongs to: (*a, *b) with angle index *i
+  if (interleaved) { *i = lane >> 1; *a = 2 * *i; *b = *a + 1; }
+  else { const int half = rot_dims >> 1; *i = lane < half ? lane : lane - half; *a = *i; *b = *i + half; }
+}
+
+template <typename T>
+__device__ __forceinline__ float rotate_lane(const T* src, int lane, const LatentPrepArgs& a, const float* cs,
+                                             const float* sn) {
+  if (lane >= a.rot_dims) return to_f<T>(src[lane]);
+  int pa, pb, i;
+  rotated_pair(lane, a.rot_dims, a.interleaved, &pa, &pb, &i);
+  const float u = to_f<T>(src[pa]), v = to_f<T>(src[pb]);
+  return lane == pa ? u * cs[i] - v * sn[i] : v * cs[i] + u * sn[i];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_prep_kernel(LatentPrepArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const T* row = (const T*)a.proj + (size_t)t * a.ld;
+  const int q_width = a.heads * (a.d + a.r);
+  const T* down = row + q_width;
+  const float* cs = a.cos_t + (size_t)t * (a.rot_dims / 2);
+  const float* sn = a.sin_t + (size_t)t * (a.rot_dims / 2);
+  const int W = a.R + a.r;
+
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < a.R; i += blockDim.x) { const float v = to_f<T>(down[i]); ss += v * v; }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)a.R + a.eps);
+
+  if (a.write_cache) {
+    const int seq = a.tok_seq[t], pos = a.tok_pos[t];
+    const int page = a.page_ids[a.page_start[seq] + page_slot_of(pos, a.page_size, a.ring_pages)];
+    T* dst = (T*)a.pool + ((size_t)page * a.page_size + (pos % a.page_size)) * W;
+    for (int i = threadIdx.x; i < a.R; i += blockDim.x) dst[i] = from_f<T>(to_f<T>(down[i]) * inv * a.norm_w[i]);
+    for (int i = threadIdx.x; i < a.r; i += blockDim.x) dst[a.R + i] = from_f<T>(rotate_lane<T>(down + a.R, i, a, cs, sn));
+  }
+  T* q_out = (T*)a.q_abs + (size_t)t * a.heads * W;
+  for (int i = threadIdx.x; i < a.heads * a.r; i += blockDim.x) {
+    const int h = i / a.r, lane = i % a.r;
+    q_out[(size_t)h * W + a.R + lane] = from_f<T>(rotate_lane<T>(row + h * (a.d + a.r) + a.d, lane, a, cs, sn));
+  }
+}
+
+extern "C" int odi_latent_prep(const LatentPrepArgs* args, int dtype, cudaStream_t stream) {
+  const LatentPrepArgs a = *args;
+  if (a.n_tokens <= 0) return 0;
+  if (a.rot_dims % 2 != 0 || a.rot_dims > a.r || a.R <= 0 || a.heads <= 0) return ODI_ERR_ARGUMENT;
+  if (dtype == 0) odi_rc = launch_pdl((latent_prep_kernel<float>), dim3(a.n_tokens), dim3(128), 0, stream, a);
+  else odi_rc = launch_pdl((latent_prep_kernel<bf16>), dim3(a.n_tokens), dim3(128), 0, stream, a);
+  return launch_status();
+}

@@ -1,0 +1,234 @@
+// Routing of a mixture of experts and the bookkeeping around its grouped products.  Everything here is fp32
+// and integer work; nothing waits for the host, so a step with routed experts can be captured in a graph.
+//
+//  route    per token: scores s = softmax(logits) over all router outputs; choice scores c = s + correction;
+//           the router outputs form `n_groups` equal groups of neighbours, a group's score is its largest c,
+//           only members of the `keep` best groups may be chosen; the `top` largest c among them are chosen
+//           (ties: the lower index); the weight of a chosen output is its s (no renormalisation).
+//  count    per (token, choice) pair whose output is a real expert: its rank among the pairs of that expert.
+//  plan     one block: the experts' offsets in the sorted order of pairs and the table of row tiles.
+//  scatter  per pair: its place in the sorted order (`pos`) and the order itself (`perm`).
+//  combine  per token: residual += sum over its choices, in the order of the choices, of weight times the
+//           expert's output row -- or times the token's own input for an identity output (index >= n_experts).
+//  gated_clamp  the experts' activation on a [tokens, 2 F] product (gate lanes, then up lanes):
+//           g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1).
+#include "common.cuh"
+
+struct RouteArgs {
+  const float* logits;      // [n_tokens, n_all]
+  const float* correction;  // [n_all] or null
+  int* ids;                 // [n_tokens, top]
+  float* weights;           // [n_tokens, top]
+  int n_tokens, n_all, n_groups, keep, top;
+};
+
+// (value, index) with "larger value, then lower index" as the order
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+}
+
+// One warp per token; shared memory: per warp n_all scores, n_all choice scores, n_groups group scores.
+__global__ void __launch_bounds__(128)
+moe_route_kernel(RouteArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= a.n_tokens) return;
+  float* s = sm + (size_t)warp * (2 * a.n_all + a.n_groups);
+  float* c = s + a.n_all;
+  float* gs = c + a.n_all;
+  const float* z = a.logits + (size_t)t * a.n_all;
+  float m = -INFINITY;
+  for (int e = lane; e < a.n_all; e += 32) m = fmaxf(m, z[e]);
+  m = warp_max(m);
+  float sum = 0.f;
+  for (int e = lane; e < a.n_all; e += 32) { const float p = expf(z[e] - m); s[e] = p; sum += p; }
+  sum = warp_sum(sum);
+  for (int e = lane; e < a.n_all; e += 32) {
+    s[e] = s[e] / sum;
+    c[e] = s[e] + (a.correction != nullptr ? a.correction[e] : 0.f);
+  }
+  __syncwarp();
+  const int per = a.n_all / a.n_groups;
+  if (a.keep < a.n_groups) {
+    for (int g = lane; g < a.n_groups; g += 32) {
+      float best = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, c[e]);
+      gs[g] = best;
+    }
+    __syncwarp();
+    // mark the `keep` best groups by setting their score to +inf, then drop the members of the others
+    for (int k = 0; k < a.keep; ++k) {
+      float v = -INFINITY; int i = 0x7fffffff;
+      for (int g = lane; g < a.n_groups; g += 32)
+        if (gs[g] != INFINITY && (gs[g] > v || (gs[g] == v && g < i))) { v = gs[g]; i = g; }
+      warp_argmax(v, i);
+      if (lane == 0 && i != 0x7fffffff) gs[i] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < a.n_all; e += 32)
+      if (gs[e / per] != INFINITY) c[e] = -INFINITY;
+    __syncwarp();
+  }
+  for (int k = 0; k < a.top; ++k) {
+    float v = -INFINITY; int i = 0x7fffffff;
+    for (int e = lane; e < a.n_all; e += 32) {
+      const float ce = c[e];
+      if (ce != -INFINITY && (i == 0x7fffffff || ce > v)) { v = ce; i = e; }   // -inf: not a candidate
+    }
+    warp_argmax(v, i);
+    if (lane == 0) {
+      const bool found = i != 0x7fffffff && v != -INFINITY;
+      a.ids[(size_t)t * a.top + k] = found ? i : -1;
+      a.weights[(size_t)t * a.top + k] = found ? s[i] : 0.f;
+      if (found) c[i] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
+extern "C" int odi_moe_route(const RouteArgs* args, cudaStream_t stream) {
+  const RouteArgs a = *args;
+  if (a.n_tokens <= 0) return 0;
+  if (a.n_all <= 0 || a.n_groups <= 0 || a.n_all % a.n_groups != 0 || a.keep <= 0 || a.keep > a.n_groups || a.top <= 0)
+    return ODI_ERR_ARGUMENT;
+  const size_t smem = sizeof(float) * 4 * (2 * (size_t)a.n_all + a.n_groups);
+  if (smem > 48 * 1024) return ODI_ERR_UNSUPPORTED;
+  odi_rc = launch_pdl(moe_route_kernel, dim3((a.n_tokens + 3) / 4), dim3(128), smem, stream, a);
+  return launch_status();
+}
+
+struct GroupingArgs {
+  const int* ids;     // [n_pairs] chosen output per pair (pair = token * top + choice); -1: none
+  int* counts;        // [n_experts], zero on entry; zero again when plan has run
+  int* rank;          // [n_pairs]
+  int* offsets;       // [n_experts + 1]
+  int* pos;           // [n_pairs] place of the pair in the sorted order (undefined for identity outputs)
+  int* perm;          // [n_pairs] the sorted order: perm[place] = pair
+  int* tile_group;    // [max_tiles]
+  int* tile_row0;
+  int* tile_rows;
+  int* n_tiles;       // [1]
+  int n_pairs, n_experts, tm, max_tiles;
+};
+
+__global__ void moe_count_kernel(GroupingArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= a.n_pairs) return;
+  const int e = a.ids[p];
+  if (e >= 0 && e < a.n_experts) a.rank[p] = atomicAdd(&a.counts[e], 1);
+}
+
+__global__ void moe_plan_kernel(GroupingArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x != 0) return;
+  int off = 0, tiles = 0;
+  for (int e = 0; e < a.n_experts; ++e) {
+    const int c = a.counts[e];
+    a.counts[e] = 0;
+    a.offsets[e] = off;
+    for (int r = 0; r < c && tiles < a.max_tiles; r += a.tm) {
+      a.tile_group[tiles] = e; a.tile_row0[tiles] = off + r; a.tile_rows[tiles] = min(a.tm, c - r);
+      ++tiles;
+    }
+    off += c;
+  }
+  a.offsets[a.n_experts] = off;
+  a.n_tiles[0] = tiles;
+}
+
+__global__ void moe_scatter_kernel(GroupingArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= a.n_pairs) return;
+  const int e = a.ids[p];
+  if (e >= 0 && e < a.n_experts) {
+    const int place = a.offsets[e] + a.rank[p];
+    a.pos[p] = place;
+    a.perm[place] = p;
+  }
+}
+
+extern "C" int odi_moe_group(const GroupingArgs* args, cudaStream_t stream) {
+  const GroupingArgs a = *args;
+  if (a.n_pairs <= 0) return 0;
+  if (a.n_experts <= 0 || a.tm <= 0 || a.max_tiles < (a.n_pairs + a.tm - 1) / a.tm + a.n_experts) return ODI_ERR_ARGUMENT;
+  const int blocks = (a.n_pairs + 255) / 256;
+  odi_rc = launch_pdl(moe_count_kernel, dim3(blocks), dim3(256), 0, stream, a);
+  if (odi_rc == 0) odi_rc = launch_pdl(moe_plan_kernel, dim3(1), dim3(32), 0, stream, a);
+  if (odi_rc == 0) odi_rc = launch_pdl(moe_scatter_kernel, dim3(blocks), dim3(256), 0, stream, a);
+  return launch_status();
+}
+
+struct CombineArgs {
+  float* residual;        // [n_tokens, H], added to in place
+  const float* expert_out;  // [n_pairs, H] rows in the sorted order
+  const void* input;      // [n_tokens, H] in T: what identity outputs pass on
+  const int* ids;
+  const float* weights;
+  const int* pos;
+  int n_tokens, H, top, n_experts;
+};
+
+template <typename T>
+__global__ void moe_combine_kernel(CombineArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < a.H; i += blockDim.x) {
+    float sum = 0.f;
+    for (int k = 0; k < a.top; ++k) {
+      const int p = t * a.top + k;
+      const int e = a.ids[p];
+      if (e < 0) continue;
+      const float v = e < a.n_experts ? a.expert_out[(size_t)a.pos[p] * a.H + i]
+                                      : to_f<T>(((const T*)a.input)[(size_t)t * a.H + i]);
+      sum = fmaf(a.weights[p], v, sum);
+    }
+    a.residual[(size_t)t * a.H + i] += sum;
+  }
+}
+
+extern "C" int odi_moe_combine(const CombineArgs* args, int dtype, cudaStream_t stream) {
+  const CombineArgs a = *args;
+  if (a.n_tokens <= 0) return 0;
+  const int threads = a.H >= 1024 ? 256 : 128;
+  if (dtype == 0) odi_rc = launch_pdl((moe_combine_kernel<float>), dim3(a.n_tokens), dim3(threads), 0, stream, a);
+  else odi_rc = launch_pdl((moe_combine_kernel<bf16>), dim3(a.n_tokens), dim3(threads), 0, stream, a);
+  return launch_status();
+}
+
+template <typename T>
+__global__ void gated_clamp_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long n, int F, float limit,
+                                   float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long row = i / F;
+  const int f = (int)(i % F);
+  const float g = fminf(to_f<T>(gate_up[row * 2 * F + f]), limit);
+  const float u = fminf(fmaxf(to_f<T>(gate_up[row * 2 * F + F + f]), -limit), limit);
+  out[i] = from_f<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+}
+
+extern "C" int odi_gated_clamp(const void* gate_up, void* out, int rows, int F, float limit, float alpha, int dtype,
+                               cudaStream_t stream) {
+  const long long n = (long long)rows * F;
+  if (n <= 0) return 0;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == 0) odi_rc = launch_pdl((gated_clamp_kernel<float>), dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)out, n, F, limit, alpha);
+  else odi_rc = launch_pdl((gated_clamp_kernel<bf16>), dim3(blocks), dim3(256), 0, stream, (const bf16*)gate_up, (bf16*)out, n, F, limit, alpha);
+  return launch_status();
+}

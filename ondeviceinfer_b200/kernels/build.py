@@ -160,7 +160,12 @@ ALL_SOURCES = {
     "sampling": [{}],
     "gemm_tcgen05": [{}, {"ODI_WAIT_CYCLES": 20_000_000}],      # the second: ops.selftest_bounded_wait
     "gemm_prefill_tcgen05": [{}],
-    "attention_simt": [{"ODI_HEAD_DIM": d} for d in _HEAD_SIZES_MMA + (512,)],
+    "attention_simt": [{"ODI_HEAD_DIM": d} for d in _HEAD_SIZES_MMA + (512,)]
+                      + [{"ODI_HEAD_DIM": 576, "ODI_VALUE_DIM": 512, "ODI_SHARED_KV": 1}],      # a latent cache
+    "latent": [{}],
+    "grouped_gemm": [{}],
+    "moe": [{}],
+    "delta": [{"ODI_DELTA_DIM": d} for d in (64, 128)],
     "attention_mma": [{"ODI_HEAD_DIM": d} for d in _HEAD_SIZES_MMA],
     "attention_tcgen05": [{"ODI_HEAD_DIM": 64}, {"ODI_HEAD_DIM": 128}],
 }

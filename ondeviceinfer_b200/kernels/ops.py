@@ -575,25 +575,42 @@ SIMT_HEAD_DIMS = tuple(range(16, 513, 16))
 
 def attention_simt(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
                    nq: int, nkv: int, d: int, page_size: int, ring_pages: int, window: int, scale: float,
-                   splits: int = 1, partial: Optional[torch.Tensor] = None) -> None:
-    """Causal GQA over the paged cache for any mixture of prompt and decode sequences."""
-    if d not in SIMT_HEAD_DIMS:
+                   splits: int = 1, partial: Optional[torch.Tensor] = None, dv: Optional[int] = None,
+                   shared_kv: bool = False) -> None:
+    """Causal GQA over the paged cache for any mixture of prompt and decode sequences.
+
+    ``dv`` (default ``d``): width of the value rows and of the output.  ``shared_kv``: a cached row is key and
+    value at once (the value is its first ``dv`` lanes; ``v_pool`` is None), as in attention over a latent
+    cache; ``d`` may then be any multiple of 4."""
+    dv = d if dv is None else dv
+    plain = dv == d and not shared_kv
+    if plain and d not in SIMT_HEAD_DIMS:
         raise KernelError(f"attention takes head sizes in steps of 16 up to 512, not {d}")
+    if not plain and (d % 4 != 0 or not 4 <= d <= 1024 or dv <= 0 or (shared_kv and dv > d)):
+        raise KernelError(f"attention with a value width of its own takes key widths in steps of 4 up to 1024 "
+                          f"and values no wider than a shared row (d={d}, dv={dv})")
     _require(q, "q")
     _require(out, "out", q.dtype)
     _require(k_pool, "k_pool", q.dtype)
-    _require(v_pool, "v_pool", q.dtype)
+    if shared_kv:
+        if v_pool is not None:
+            raise KernelError("attention over shared rows takes no value pool")
+    else:
+        _require(v_pool, "v_pool", q.dtype)
     n_tokens = q.numel() // (nq * d)
-    if out.numel() != q.numel():
+    if out.numel() != n_tokens * nq * dv:
         raise KernelError("q and out disagree")
     if splits > 1:
-        need = n_tokens * nq * splits * (d + 2)
+        need = n_tokens * nq * splits * (dv + 2)
         if partial is None or partial.numel() < need or partial.dtype != torch.float32:
             raise KernelError(f"splits={splits} needs an fp32 partial buffer of {need} elements")
     args = _AttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(partial), _ptr(cu_q), _ptr(past),
                      _ptr(page_start), _ptr(page_ids), n_seqs, nq, nkv, page_size, ring_pages, window, splits,
                      0, 0, scale)
-    lib = load_library("attention_simt", {"ODI_HEAD_DIM": d})
+    defines = {"ODI_HEAD_DIM": d}
+    if not plain:
+        defines.update({"ODI_VALUE_DIM": dv, "ODI_SHARED_KV": 1 if shared_kv else 0})
+    lib = load_library("attention_simt", defines)
     _check(lib.odi_attention_simt(byref(args), c_int(max_q_len), c_int(n_tokens), c_int(dtype_code(q.dtype)),
                                   _stream()), "attention_simt", 2 if splits > 1 else 1)
 
@@ -819,10 +836,275 @@ def attention_tcgen05(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, 
            "attention_tcgen05")
 
 
+# ------------------------------------------------------------------------------ norms and activations in fp32
+
+
+def rmsnorm_scaled(x: torch.Tensor, scale: torch.Tensor, eps: float, out: torch.Tensor,
+                   rows: Optional[torch.Tensor] = None) -> None:
+    """out[i] = cast(x[r_i] * rsqrt(mean(x[r_i]^2) + eps) * scale): the scaling in fp32, one rounding."""
+    _require(x, "x", torch.float32, 2)
+    _require(scale, "scale", torch.float32, 1)
+    _require(out, "out", ndim=2)
+    n, H = out.shape
+    if scale.numel() != H or x.shape[1] != H:
+        raise KernelError(f"rmsnorm sizes disagree: x {tuple(x.shape)}, scale {tuple(scale.shape)}, out {tuple(out.shape)}")
+    if rows is not None:
+        _require(rows, "rows", torch.int32, 1)
+        if rows.numel() != n:
+            raise KernelError("rows and out disagree")
+    elif x.shape[0] != n:
+        raise KernelError("x and out disagree")
+    lib = load_library("elementwise")
+    _check(lib.odi_rmsnorm_scaled(_ptr(x), _ptr(scale), _ptr(out), _ptr(rows), c_int(n), c_int(H), c_float(eps),
+                                  c_int(dtype_code(out.dtype)), _stream()), "rmsnorm_scaled")
+
+
+def gated_clamp(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+    """out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), for
+    ``gate_up`` [tokens, 2 F] (gate lanes, then up lanes)."""
+    _require(gate_up, "gate_up", ndim=2)
+    _require(out, "out", gate_up.dtype, 2)
+    rows, F = out.shape
+    if gate_up.shape != (rows, 2 * F):
+        raise KernelError(f"gated_clamp sizes disagree: {tuple(gate_up.shape)} -> {tuple(out.shape)}")
+    lib = load_library("moe")
+    _check(lib.odi_gated_clamp(_ptr(gate_up), _ptr(out), c_int(rows), c_int(F), c_float(limit), c_float(alpha),
+                               c_int(dtype_code(out.dtype)), _stream()), "gated_clamp")
+
+
+# ------------------------------------------------------------------------------ latent attention
+
+
+class _LatentPrepArgs(Structure):
+    _fields_ = [("proj", c_void_p), ("q_abs", c_void_p), ("pool", c_void_p), ("norm_w", c_void_p),
+                ("cos_t", c_void_p), ("sin_t", c_void_p), ("tok_seq", c_void_p), ("tok_pos", c_void_p),
+                ("page_start", c_void_p), ("page_ids", c_void_p),
+                ("n_tokens", c_int), ("ld", c_int), ("heads", c_int), ("d", c_int), ("r", c_int), ("R", c_int),
+                ("rot_dims", c_int), ("interleaved", c_int), ("page_size", c_int), ("ring_pages", c_int),
+                ("write_cache", c_int), ("eps", c_float)]
+
+
+def latent_prep(proj: torch.Tensor, q_abs: torch.Tensor, pool: torch.Tensor, norm_w: torch.Tensor, cos_t, sin_t,
+                tok_seq, tok_pos, page_start, page_ids, *, heads: int, d: int, r: int, R: int, rot_dims: int,
+                interleaved: bool, page_size: int, ring_pages: int, write_cache: bool, eps: float) -> None:
+    """From the fused query / down projection ``proj`` [tokens, heads (d + r) + R + r]: the normed latent and the
+    rotated shared key lanes into the token's cache row, each head's rotated query lanes into lanes R.. of
+    ``q_abs`` [tokens, heads, R + r] (see ``csrc/latent.cu``)."""
+    _require(proj, "proj", ndim=2)
+    _require(q_abs, "q_abs", proj.dtype)
+    _require(pool, "pool", proj.dtype)
+    _require(norm_w, "norm_w", torch.float32, 1)
+    n = proj.shape[0]
+    if proj.shape[1] != heads * (d + r) + R + r or q_abs.numel() != n * heads * (R + r) or norm_w.numel() != R:
+        raise KernelError("latent_prep sizes disagree")
+    if rot_dims > 0:
+        _require(cos_t, "cos_t", torch.float32, 2)
+        _require(sin_t, "sin_t", torch.float32, 2)
+        if cos_t.shape != (n, rot_dims // 2) or sin_t.shape != cos_t.shape:
+            raise KernelError("rotary tables do not fit the tokens")
+    args = _LatentPrepArgs(_ptr(proj), _ptr(q_abs), _ptr(pool), _ptr(norm_w), _ptr(cos_t), _ptr(sin_t), _ptr(tok_seq),
+                           _ptr(tok_pos), _ptr(page_start), _ptr(page_ids), n, proj.shape[1], heads, d, r, R, rot_dims,
+                           1 if interleaved else 0, page_size, ring_pages, 1 if write_cache else 0, eps)
+    lib = load_library("latent")
+    _check(lib.odi_latent_prep(byref(args), c_int(dtype_code(proj.dtype)), _stream()), "latent_prep")
+
+
+# ------------------------------------------------------------------------------ grouped products and routing
+
+
+class _GroupedArgs(Structure):
+    _fields_ = [("A", c_void_p), ("W", c_void_p), ("C", c_void_p), ("row_index", c_void_p), ("tile_group", c_void_p),
+                ("tile_row0", c_void_p), ("tile_rows", c_void_p), ("n_tiles", c_void_p),
+                ("a_group_off", ctypes.c_longlong), ("w_group_stride", ctypes.c_longlong), ("c_group_off", ctypes.c_longlong),
+                ("lda", c_int), ("ldw", c_int), ("ldc", c_int), ("M", c_int), ("N", c_int), ("K", c_int),
+                ("groups", c_int), ("index_div", c_int), ("epi", c_int), ("limit", c_float), ("alpha", c_float)]
+
+
+GROUPED_STORE, GROUPED_STORE_F32, GROUPED_GATED_CLAMP = 0, 1, 2
+
+
+def grouped_rows_tile(rows_per_group: float) -> int:
+    """Row tile of the grouped product for groups of about this many rows: 16 or 64."""
+    return 64 if rows_per_group > 32 else 16
+
+
+def grouped_gemm_heads(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, a_col: int, a_stride: int, c_col: int,
+                       c_stride: int, K: int, out_f32: bool = False) -> None:
+    """One product per head in one launch: for head g, ``c[:, c_col + g c_stride : +N] = a[:, a_col + g a_stride :
+    +K] w[g]^T`` with ``w`` [heads, N, K]; ``a`` and ``c`` are 2-D and contiguous, fp32 accumulation in k order."""
+    _require(a, "a", w.dtype, 2)
+    _require(w, "w", ndim=3)
+    _require(c, "c", torch.float32 if out_f32 else w.dtype, 2)
+    groups, N, Kw = w.shape
+    M = a.shape[0]
+    if Kw != K or c.shape[0] != M or a_col + (groups - 1) * a_stride + K > a.shape[1] \
+            or c_col + (groups - 1) * c_stride + N > c.shape[1]:
+        raise KernelError(f"grouped product sizes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, c {tuple(c.shape)}")
+    args = _GroupedArgs(a.data_ptr() + a_col * a.element_size(), _ptr(w), c.data_ptr() + c_col * c.element_size(),
+                        None, None, None, None, None, a_stride, N * K, c_stride, a.shape[1], K, c.shape[1], M, N, K,
+                        groups, 1, GROUPED_STORE_F32 if out_f32 else GROUPED_STORE, 0.0, 0.0)
+    lib = load_library("grouped_gemm")
+    _check(lib.odi_grouped_gemm(byref(args), c_int(0), c_int(grouped_rows_tile(M)), c_int(dtype_code(w.dtype)),
+                                _stream()), "grouped_gemm")
+
+
+def grouped_gemm_routed(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, table: "RoutingTable", *, gather: bool,
+                        epi: int, limit: float = 0.0, alpha: float = 0.0) -> None:
+    """The product of each routed row with its expert's matrix ``w[e]`` ([experts, rows, K]; with
+    ``GROUPED_GATED_CLAMP`` rows = N gate rows then N up rows).  Rows are taken in ``table``'s sorted order; with
+    ``gather`` row i reads ``a[perm[i] // top]`` (the token's input), else ``a[i]``; row i of ``c`` is written."""
+    _require(a, "a", w.dtype, 2)
+    _require(w, "w", ndim=3)
+    _require(c, "c", torch.float32 if epi == GROUPED_STORE_F32 else w.dtype, 2)
+    experts, w_rows, K = w.shape
+    N = w_rows // 2 if epi == GROUPED_GATED_CLAMP else w_rows
+    if a.shape[1] != K or c.shape != (table.n_pairs, N) or experts != table.n_experts:
+        raise KernelError(f"routed product sizes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, c {tuple(c.shape)}")
+    args = _GroupedArgs(_ptr(a), _ptr(w), _ptr(c), _ptr(table.perm) if gather else None, _ptr(table.tile_group),
+                        _ptr(table.tile_row0), _ptr(table.tile_rows), _ptr(table.n_tiles), 0, w_rows * K, 0,
+                        K, K, N, 0, N, K, experts, table.top if gather else 1, epi, limit, alpha)
+    lib = load_library("grouped_gemm")
+    _check(lib.odi_grouped_gemm(byref(args), c_int(table.max_tiles), c_int(table.tm), c_int(dtype_code(w.dtype)),
+                                _stream()), "grouped_gemm")
+
+
+class _RouteArgs(Structure):
+    _fields_ = [("logits", c_void_p), ("correction", c_void_p), ("ids", c_void_p), ("weights", c_void_p),
+                ("n_tokens", c_int), ("n_all", c_int), ("n_groups", c_int), ("keep", c_int), ("top", c_int)]
+
+
+def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], ids: torch.Tensor, weights: torch.Tensor, *,
+              n_groups: int, keep: int) -> None:
+    """Grouped top-k routing of fp32 ``logits`` [tokens, outputs] (see ``csrc/moe.cu``): ``ids`` and ``weights``
+    [tokens, top] receive the chosen outputs, best first, and their softmax scores."""
+    _require(logits, "logits", torch.float32, 2)
+    _require(ids, "ids", torch.int32, 2)
+    _require(weights, "weights", torch.float32, 2)
+    n, n_all = logits.shape
+    if ids.shape[0] != n or weights.shape != ids.shape:
+        raise KernelError("routing outputs do not fit the tokens")
+    if correction is not None:
+        _require(correction, "correction", torch.float32, 1)
+        if correction.numel() != n_all:
+            raise KernelError("the correction has one entry per router output")
+    args = _RouteArgs(_ptr(logits), _ptr(correction), _ptr(ids), _ptr(weights), n, n_all, n_groups, keep, ids.shape[1])
+    lib = load_library("moe")
+    _check(lib.odi_moe_route(byref(args), _stream()), "moe_route")
+
+
+class _GroupingArgs(Structure):
+    _fields_ = [("ids", c_void_p), ("counts", c_void_p), ("rank", c_void_p), ("offsets", c_void_p), ("pos", c_void_p),
+                ("perm", c_void_p), ("tile_group", c_void_p), ("tile_row0", c_void_p), ("tile_rows", c_void_p),
+                ("n_tiles", c_void_p), ("n_pairs", c_int), ("n_experts", c_int), ("tm", c_int), ("max_tiles", c_int)]
+
+
+class RoutingTable:
+    """The (token, choice) pairs of a step sorted by expert, made on the device by :func:`moe_group`: ``perm`` the
+    sorted order, ``pos`` each pair's place in it, and the table of row tiles the grouped products walk."""
+
+    def __init__(self, n_tokens: int, top: int, n_experts: int, device) -> None:
+        self.n_pairs, self.top, self.n_experts = n_tokens * top, top, n_experts
+        self.tm = grouped_rows_tile(self.n_pairs / max(n_experts, 1))
+        self.max_tiles = -(-self.n_pairs // self.tm) + n_experts
+        ints = torch.empty(3 * self.n_pairs + n_experts + 1 + 3 * self.max_tiles + 1, dtype=torch.int32, device=device)
+        cuts = [self.n_pairs, self.n_pairs, self.n_pairs, n_experts + 1, self.max_tiles, self.max_tiles, self.max_tiles, 1]
+        (self.rank, self.pos, self.perm, self.offsets, self.tile_group, self.tile_row0, self.tile_rows,
+         self.n_tiles) = torch.split(ints, cuts)
+
+
+def moe_group(ids: torch.Tensor, counts: torch.Tensor, table: RoutingTable) -> None:
+    """Fill ``table`` from the chosen outputs ``ids`` [tokens, top]; outputs >= ``table.n_experts`` (identity
+    outputs) and -1 take no place.  ``counts`` [experts] int32 must be zero and is zero again afterwards."""
+    _require(ids, "ids", torch.int32, 2)
+    _require(counts, "counts", torch.int32, 1)
+    if ids.numel() != table.n_pairs or counts.numel() != table.n_experts:
+        raise KernelError("the routing table was made for other sizes")
+    args = _GroupingArgs(_ptr(ids), _ptr(counts), _ptr(table.rank), _ptr(table.offsets), _ptr(table.pos),
+                         _ptr(table.perm), _ptr(table.tile_group), _ptr(table.tile_row0), _ptr(table.tile_rows),
+                         _ptr(table.n_tiles), table.n_pairs, table.n_experts, table.tm, table.max_tiles)
+    lib = load_library("moe")
+    _check(lib.odi_moe_group(byref(args), _stream()), "moe_group", 3)
+
+
+class _CombineArgs(Structure):
+    _fields_ = [("residual", c_void_p), ("expert_out", c_void_p), ("input", c_void_p), ("ids", c_void_p),
+                ("weights", c_void_p), ("pos", c_void_p), ("n_tokens", c_int), ("H", c_int), ("top", c_int),
+                ("n_experts", c_int)]
+
+
+def moe_combine(residual: torch.Tensor, expert_out: torch.Tensor, x: torch.Tensor, ids: torch.Tensor,
+                weights: torch.Tensor, table: RoutingTable) -> None:
+    """residual[t] += sum_k weights[t, k] * (row pos[t, k] of ``expert_out``, or ``x[t]`` for an identity output)."""
+    _require(residual, "residual", torch.float32, 2)
+    _require(expert_out, "expert_out", torch.float32, 2)
+    _require(x, "x", ndim=2)
+    n, H = residual.shape
+    if x.shape != (n, H) or expert_out.shape != (table.n_pairs, H) or ids.numel() != table.n_pairs:
+        raise KernelError("moe_combine sizes disagree")
+    args = _CombineArgs(_ptr(residual), _ptr(expert_out), _ptr(x), _ptr(ids), _ptr(weights), _ptr(table.pos), n, H,
+                        table.top, table.n_experts)
+    lib = load_library("moe")
+    _check(lib.odi_moe_combine(byref(args), c_int(dtype_code(x.dtype)), _stream()), "moe_combine")
+
+
+# ------------------------------------------------------------------------------ the gated delta rule
+
+
+class _DeltaArgs(Structure):
+    _fields_ = [("proj", c_void_p), ("taps", c_void_p), ("conv_state", c_void_p), ("conv_out", c_void_p),
+                ("decay_in", c_void_p), ("a_log", c_void_p), ("dt_bias", c_void_p), ("qkg", c_void_p), ("beta", c_void_p),
+                ("state", c_void_p), ("o", c_void_p), ("norm_w", c_void_p), ("out", c_void_p), ("cu_q", c_void_p),
+                ("tok_seq", c_void_p), ("slots", c_void_p),
+                ("n_tokens", c_int), ("n_seqs", c_int), ("ld_proj", c_int), ("ld_decay", c_int), ("heads", c_int),
+                ("kv_heads", c_int), ("dv", c_int), ("taps_n", c_int), ("C", c_int), ("eps", c_float),
+                ("unit_eps", c_float)]
+
+
+DELTA_MAX_DIM = 480     # the recurrence stages 8 tokens of q, k and decay in 48 KB of shared memory
+
+
+def delta_rule(proj: torch.Tensor, decay_in: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor,
+               dt_bias: torch.Tensor, norm_w: torch.Tensor, conv_state: Optional[torch.Tensor], state: torch.Tensor,
+               out: torch.Tensor, cu_q, tok_seq, slots, *, n_seqs: int, heads: int, kv_heads: int, d: int, dv: int,
+               eps: float, unit_eps: float) -> None:
+    """The channel-wise gated delta rule between its input products and its output product (``csrc/delta.cu``).
+
+    ``proj`` [tokens, C + heads]: q, k and v channels before their convolutions (C = 2 kv_heads d + heads dv), then
+    one beta logit per head.  ``decay_in`` fp32 [tokens, heads d + heads dv]: the decay's inner term per head and
+    key channel, then the output gate's logits.  ``taps`` fp32 [C, K].  ``conv_state`` fp32 [slots, K - 1, C] and
+    ``state`` fp32 [slots, heads, d, dv] are read and advanced for the sequences ``slots``.  ``out`` [tokens,
+    heads dv] receives the gated, normed read-outs in the dtype of ``proj``."""
+    _require(proj, "proj", ndim=2)
+    _require(decay_in, "decay_in", torch.float32, 2)
+    _require(taps, "taps", torch.float32, 2)
+    _require(state, "state", torch.float32)
+    _require(out, "out", proj.dtype, 2)
+    n = proj.shape[0]
+    C, K = taps.shape
+    if not 1 <= d <= DELTA_MAX_DIM:
+        raise KernelError(f"the delta rule takes key sizes up to {DELTA_MAX_DIM}, not {d}")
+    if (C != 2 * kv_heads * d + heads * dv or proj.shape[1] != C + heads or decay_in.shape != (n, heads * (d + dv))
+            or out.shape != (n, heads * dv) or a_log.numel() != heads or dt_bias.numel() != heads * d
+            or norm_w.numel() != dv or tuple(state.shape[1:]) != (heads, d, dv)):
+        raise KernelError("delta_rule sizes disagree")
+    if K > 1:
+        _require(conv_state, "conv_state", torch.float32)
+        if tuple(conv_state.shape[1:]) != (K - 1, C):
+            raise KernelError("the convolution state does not fit the taps")
+    dev = proj.device
+    conv_out = torch.empty((n, C), dtype=proj.dtype, device=dev)
+    qkg = torch.empty((n, heads, 3, d), dtype=torch.float32, device=dev)
+    beta = torch.empty((n, heads), dtype=torch.float32, device=dev)
+    o = torch.empty((n, heads * dv), dtype=torch.float32, device=dev)
+    args = _DeltaArgs(_ptr(proj), _ptr(taps), _ptr(conv_state), _ptr(conv_out), _ptr(decay_in), _ptr(a_log),
+                      _ptr(dt_bias), _ptr(qkg), _ptr(beta), _ptr(state), _ptr(o), _ptr(norm_w), _ptr(out), _ptr(cu_q),
+                      _ptr(tok_seq), _ptr(slots), n, n_seqs, proj.shape[1], decay_in.shape[1], heads, kv_heads, dv, K, C,
+                      eps, unit_eps)
+    lib = load_library("delta", {"ODI_DELTA_DIM": d})
+    _check(lib.odi_delta_rule(byref(args), c_int(dtype_code(proj.dtype)), _stream()), "delta_rule", 6 if K > 1 else 5)
+
+
 # ------------------------------------------------------------------------------ sampling
-
-
-_sample_state = {}
 
 
 def _sample_buffers(device, rows: int, chunks: int):

@@ -1,7 +1,10 @@
 from .base import Part, Runtime, build_part, register_part
 from .linear import gated_linear, linear
-from . import norm, position, attention, mlp, block, embedding  # noqa: F401  (registers the built-in parts)
+from . import norm, position, attention, mlp, block, embedding, latent_attention, channel_delta, routed_experts  # noqa: F401  (registers the built-in parts)
 from .attention import Attention
+from .channel_delta import ChannelDelta
+from .latent_attention import LatentAttention
+from .routed_experts import RoutedExperts
 from .embedding import OutputHead, TokenEmbedding
 from .block import PreNormBlock
 from .mlp import GatedMLP
@@ -9,4 +12,4 @@ from .norm import RMSNorm
 from .position import NoPosition, Rotary
 
 __all__ = ["Part", "Runtime", "build_part", "register_part", "linear", "gated_linear", "Attention", "PreNormBlock",
-           "GatedMLP", "RMSNorm", "NoPosition", "Rotary", "TokenEmbedding", "OutputHead"]
+           "GatedMLP", "LatentAttention", "ChannelDelta", "RoutedExperts", "RMSNorm", "NoPosition", "Rotary", "TokenEmbedding", "OutputHead"]

@@ -39,6 +39,8 @@ class Attention(Part):
         if spec.window is not None and spec.window <= 0:
             raise ValueError("window must be positive")
         self.position = build_part(spec.position)
+        if getattr(self.position, "interleaved", False):
+            raise ValueError("this attention's head preparation rotates half-split pairs only")
         self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(spec.head_dim)
 
     # ------------------------------------------------------------------ tensors

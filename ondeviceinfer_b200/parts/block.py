@@ -12,7 +12,8 @@ def ops_residual_add(residual, product) -> None:
 
 
 class PreNormBlock(Part):
-    """h += mixer(norm(h)); h += feed_forward(norm(h))  (ondeviceinfer/model.py:49-63)."""
+    """h += mixer(norm(h)); h += feed_forward(norm(h))  (ondeviceinfer/model.py:49-63); the second half is
+    left out for a spec without a feed-forward."""
 
     finishes_residual_adds = True     # its norms take over a residual add that a product left pending
 
@@ -20,11 +21,12 @@ class PreNormBlock(Part):
         super().__init__(spec)
         self.mixer_norm = build_part(spec.mixer_norm)
         self.mixer = build_part(spec.mixer)
-        self.ffn_norm = build_part(spec.ffn_norm)
-        self.ffn = build_part(spec.ffn)
+        # a layer without a feed-forward has neither the part nor its norm
+        self.ffn_norm = build_part(spec.ffn_norm) if spec.ffn is not None else None
+        self.ffn = build_part(spec.ffn) if spec.ffn is not None else None
 
     def _children(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        return tuple(part for part in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if part is not None)
 
     def tensor_decls(self):
         return [d for part in self._children() for d in part.tensor_decls()]
@@ -55,7 +57,7 @@ class PreNormBlock(Part):
             if pending[0] is hidden and getattr(norm, "adds", False):
                 return norm(hidden, add=pending[1])
             ops_residual_add(*pending)
-        if known is not None and known[0] is hidden and hasattr(norm, "lazy") and getattr(consumer, "takes_lazy_norm", False):
+        if known is not None and known[0] is hidden and getattr(norm, "lazy", None) is not None and getattr(consumer, "takes_lazy_norm", False):
             return norm.lazy(hidden, known[1])
         return norm(hidden)
 
@@ -64,7 +66,8 @@ class PreNormBlock(Part):
         # here or in the next block; the model flushes the last one): it says so, and only then is an add deferred.
         ctx.defers_residual_add = True
         self.mixer.forward(self._normed(self.mixer_norm, self.mixer, hidden, ctx), ctx, view, hidden)
-        self.ffn.forward(self._normed(self.ffn_norm, self.ffn, hidden, ctx), ctx, hidden)
+        if self.ffn is not None:
+            self.ffn.forward(self._normed(self.ffn_norm, self.ffn, hidden, ctx), ctx, hidden)
 
 
 register_part(PreNormBlockSpec, PreNormBlock)

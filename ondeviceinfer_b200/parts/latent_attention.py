@@ -1,0 +1,113 @@
+"""Latent attention: causal attention over a compressed cache of one latent row per position.
+
+The cache row of a position is ``[c | k_rot]``: the normed latent (``kv_rank`` lanes) and the rotated key lanes
+that all heads share.  Keys and values are never expanded.  Since a head's plain key is ``W_uk c`` and its
+value ``W_uv c``, the score ``q_plain . W_uk c + q_rot . k_rot`` equals ``[W_uk^T q_plain | q_rot] . [c | k_rot]``
+and the output ``W_uv sum_j p_j c_j``: the key up-projection is folded into the query, attention runs with one
+shared key/value row per position (the value being the row's first ``kv_rank`` lanes), and the value
+up-projection is applied to the attention's output.  Steps of ``forward``:
+
+1. one product for the query and the down projection;
+2. head preparation (``csrc/latent.cu``): latent norm, rotation, cache write, rotated query lanes;
+3. a product per head that folds ``W_uk`` into the plain query lanes (``csrc/grouped_gemm.cu``);
+4. attention over the cache pages (``csrc/attention_simt.cu`` built for shared rows), split over the keys
+   for single-token steps;
+5. a product per head with ``W_uv``, then the output projection with the residual add.
+
+Scores, softmax, the latent norm and the angles are fp32 in both compute dtypes.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache import PAGE_SIZE, KVNeed
+from ..config.specs import LatentAttentionSpec
+from ..kernels import ops
+from ..weights.tensors import TensorDecl
+from .base import Part, build_part, register_part
+from .linear import linear
+
+
+class LatentAttention(Part):
+    graph_safe = True   # no host work that depends on the step's values
+
+    def __init__(self, spec: LatentAttentionSpec) -> None:
+        super().__init__(spec)
+        for key in ("num_heads", "qk_dim", "v_dim", "kv_rank"):
+            if getattr(spec, key) <= 0:
+                raise ValueError(f"{key} must be positive, got {getattr(spec, key)}")
+        if spec.rot_dim < 0 or (spec.kv_rank + spec.rot_dim) % 4 != 0:
+            raise ValueError(f"kv_rank + rot_dim must be a multiple of 4 (got {spec.kv_rank} + {spec.rot_dim}): "
+                             "the attention kernel reads cache rows four lanes at a time")
+        self.position = build_part(spec.position)
+        if self.position.rot_dim > spec.rot_dim:
+            raise ValueError("the position encoding rotates more lanes than the heads have rotated lanes")
+        self.row = spec.kv_rank + spec.rot_dim        # width of a cache row and of an absorbed query
+
+    def tensor_decls(self):
+        s = self.spec
+        q = s.num_heads * (s.qk_dim + s.rot_dim)
+        return [TensorDecl(s.name("q"), (q, s.hidden_size)),
+                TensorDecl(s.name("dkv"), (s.kv_rank + s.rot_dim, s.hidden_size)),
+                TensorDecl(s.name("dkv_norm"), (s.kv_rank,), "one_plus_normal"),
+                TensorDecl(s.name("uk"), (s.num_heads * s.qk_dim, s.kv_rank)),
+                TensorDecl(s.name("uv"), (s.num_heads * s.v_dim, s.kv_rank)),
+                TensorDecl(s.name("o"), (s.hidden_size, s.num_heads * s.v_dim))] + self.position.tensor_decls()
+
+    def load(self, fetch, runtime) -> None:
+        s = self.spec
+        self.runtime = runtime
+        self.w_in = torch.cat([fetch.matrix(s.name("q")), fetch.matrix(s.name("dkv"))], 0)
+        self.latent_norm = fetch.vector(s.name("dkv_norm"))
+        # per head: [kv_rank, qk_dim] so that q_plain W gives the query in latent lanes; [v_dim, kv_rank] as stored
+        self.w_uk_t = fetch.matrix(s.name("uk")).view(s.num_heads, s.qk_dim, s.kv_rank).transpose(1, 2).contiguous()
+        self.w_uv = fetch.matrix(s.name("uv")).view(s.num_heads, s.v_dim, s.kv_rank).contiguous()
+        self.w_o = fetch.matrix(s.name("o"))
+        self.position.load(fetch, runtime)
+
+    def cache_needs(self):
+        return (KVNeed(1, self.row, None, value_plane=False),)
+
+    def forward(self, x, ctx, view, residual) -> None:
+        s = self.spec
+        n = x.shape[0]
+        group = view.kv_group
+        page_start, page_ids = ctx.page_table(group.index)
+        proj = linear(x, self.w_in)
+        tables = self.position.rotary_tables(ctx)
+        cos, sin = tables if tables is not None else (None, None)
+        q_abs = torch.empty((n, s.num_heads * self.row), dtype=proj.dtype, device=proj.device)
+        ops.latent_prep(proj, q_abs, view.keys, self.latent_norm, cos, sin, ctx.tok_seq, ctx.tok_pos, page_start,
+                        page_ids, heads=s.num_heads, d=s.qk_dim, r=s.rot_dim, R=s.kv_rank,
+                        rot_dims=self.position.rot_dim if cos is not None else 0,
+                        interleaved=getattr(self.position, "interleaved", False), page_size=PAGE_SIZE,
+                        ring_pages=group.ring_pages, write_cache=view.writes_kv, eps=s.norm_eps)
+        ops.grouped_gemm_heads(proj, self.w_uk_t, q_abs, a_col=0, a_stride=s.qk_dim + s.rot_dim, c_col=0,
+                               c_stride=self.row, K=s.qk_dim)
+        latent_out = self.attend(q_abs, ctx, view, page_start, page_ids)
+        heads_out = torch.empty((n, s.num_heads * s.v_dim), dtype=proj.dtype, device=proj.device)
+        ops.grouped_gemm_heads(latent_out, self.w_uv, heads_out, a_col=0, a_stride=s.kv_rank, c_col=0,
+                               c_stride=s.v_dim, K=s.kv_rank)
+        linear(heads_out, self.w_o, residual=residual, track=ctx)
+
+    def attend(self, q_abs, ctx, view, page_start, page_ids):
+        """[tokens, heads * kv_rank]: per head the softmax-weighted sum of the latents it sees."""
+        s = self.spec
+        out = torch.empty((ctx.n_tokens, s.num_heads * s.kv_rank), dtype=q_abs.dtype, device=q_abs.device)
+        splits, partial = 1, None
+        if ctx.max_q_len == 1:
+            # single tokens: cut long key ranges so that enough blocks run side by side
+            blocks = ctx.n_seqs * ((s.num_heads + 15) // 16)
+            splits = max(1, min(32, 296 // max(blocks, 1), (ctx.max_kv_len + 255) // 256))
+            if splits > 1:
+                partial = torch.empty((ctx.n_tokens * s.num_heads * splits * (s.kv_rank + 2),), dtype=torch.float32,
+                                      device=q_abs.device)
+        ops.attention_simt(q_abs, view.keys, None, out, ctx.cu_q, ctx.past, page_start, page_ids, n_seqs=ctx.n_seqs,
+                           max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=1, d=self.row, dv=s.kv_rank, shared_kv=True,
+                           page_size=PAGE_SIZE, ring_pages=view.kv_group.ring_pages, window=0, scale=s.scale,
+                           splits=splits, partial=partial)
+        return out
+
+
+register_part(LatentAttentionSpec, LatentAttention)

@@ -16,14 +16,23 @@ class RMSNorm(Part):
     adds = True         # __call__ takes `add`: a pending residual add done in the norm's own pass
 
     """weight * cast(x * rsqrt(mean(x^2) + eps)): statistics in fp32, cast to the compute
-    dtype before the multiplication by the weight."""
+    dtype before the multiplication by the weight.  With ``scale_in_fp32`` the row is scaled in fp32 and
+    rounded once; ``weight_offset`` is added to the stored weight (in fp32, at load)."""
+
+    def __init__(self, spec: RMSNormSpec) -> None:
+        super().__init__(spec)
+        if spec.scale_in_fp32:
+            self.lazy = None      # the product prologue that norms rows itself rounds before it scales
 
     def tensor_decls(self):
-        return [TensorDecl(self.spec.weight_name, (self.spec.size,), "one_plus_normal")]
+        return [TensorDecl(self.spec.weight_name, (self.spec.size,),
+                           "one_plus_normal" if self.spec.weight_offset == 0.0 else "normal")]
 
     def load(self, fetch, runtime) -> None:
         self.runtime = runtime
         self.weight = fetch.vector(self.spec.weight_name)
+        if self.spec.weight_offset != 0.0:
+            self.weight = self.weight + self.spec.weight_offset
 
     def lazy(self, x: torch.Tensor, parts: torch.Tensor):
         """The norm of the whole of ``x`` as a :class:`~ondeviceinfer_b200.parts.linear.NormedRows`:
@@ -36,10 +45,14 @@ class RMSNorm(Part):
         the same pass when the kernel can, else beforehand."""
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.spec.size), dtype=self.runtime.dtype, device=x.device)
-        if add is not None and not (rows is None and ops.rmsnorm_adds(x, self.weight, out, add)):
+        if add is not None and (self.spec.scale_in_fp32 or
+                                not (rows is None and ops.rmsnorm_adds(x, self.weight, out, add))):
             ops.residual_add(x, add)
             add = None
-        ops.rmsnorm(x, self.weight, self.spec.eps, out, rows, add=add)
+        if self.spec.scale_in_fp32:
+            ops.rmsnorm_scaled(x, self.weight, self.spec.eps, out, rows)
+        else:
+            ops.rmsnorm(x, self.weight, self.spec.eps, out, rows, add=add)
         return out
 
 

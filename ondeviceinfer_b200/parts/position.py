@@ -22,6 +22,7 @@ class Rotary(Part):
         if spec.dim % 2 != 0 or spec.dim > spec.head_dim or spec.dim <= 0:
             raise ValueError(f"rotary_dim must be even and at most head_dim, got {spec.dim} of {spec.head_dim}")
         self.rot_dim = spec.dim
+        self.interleaved = spec.interleaved     # which lanes pair up; the tables are the same either way
 
     def load(self, fetch, runtime) -> None:
         self.runtime = runtime

@@ -1,0 +1,94 @@
+"""Mixture of experts: a grouped top-k router, clamped gated experts, identity outputs and a shared expert.
+
+Steps of ``forward`` (no step waits for the host):
+
+1. router logits in fp32 (one product), then ``ops.moe_route``: softmax over all outputs, the correction for the
+   choice only, the best groups, the top-k outputs and their scores as weights;
+2. ``ops.moe_group``: the (token, choice) pairs that go to real experts, sorted by expert on the device;
+3. two grouped products over that order (``csrc/grouped_gemm.cu``): gate and up with the clamped activation,
+   then down into fp32 rows;
+4. ``ops.moe_combine``: each token adds its weighted rows, in the order of its choices, and its own input for
+   an identity output;
+5. the shared expert, if any: gate/up product, the same activation with its own limit, down with the residual add.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import RoutedExpertsSpec
+from ..kernels import ops
+from ..weights.tensors import TensorDecl
+from .base import Part, register_part
+from .linear import linear
+
+
+class RoutedExperts(Part):
+    graph_safe = True   # no host work that depends on the step's values
+
+    def __init__(self, spec: RoutedExpertsSpec) -> None:
+        super().__init__(spec)
+        n_all = spec.num_experts + spec.num_identity
+        if spec.num_experts < 0 or spec.num_identity < 0 or n_all <= 0:
+            raise ValueError("a router needs at least one output")
+        if spec.num_groups <= 0 or n_all % spec.num_groups != 0:
+            raise ValueError(f"{n_all} router outputs do not form {spec.num_groups} equal groups")
+        if not 0 < spec.keep_groups <= spec.num_groups:
+            raise ValueError("keep_groups must be between 1 and the number of groups")
+        if not 0 < spec.top_k <= spec.keep_groups * (n_all // spec.num_groups):
+            raise ValueError("top_k exceeds the outputs that the kept groups hold")
+        self.n_all = n_all
+
+    def tensor_decls(self):
+        s = self.spec
+        decls = [TensorDecl(s.prefix + "router", (self.n_all, s.hidden_size))]
+        if s.has_correction:
+            decls.append(TensorDecl(s.prefix + "correction", (self.n_all,), "zeros"))
+        for e in range(s.num_experts):
+            decls += [TensorDecl(f"{s.prefix}e{e}.gate", (s.expert_size, s.hidden_size)),
+                      TensorDecl(f"{s.prefix}e{e}.up", (s.expert_size, s.hidden_size)),
+                      TensorDecl(f"{s.prefix}e{e}.down", (s.hidden_size, s.expert_size))]
+        if s.shared_size > 0:
+            decls += [TensorDecl(s.prefix + "shared.gate", (s.shared_size, s.hidden_size)),
+                      TensorDecl(s.prefix + "shared.up", (s.shared_size, s.hidden_size)),
+                      TensorDecl(s.prefix + "shared.down", (s.hidden_size, s.shared_size))]
+        return decls
+
+    def load(self, fetch, runtime) -> None:
+        s = self.spec
+        self.runtime = runtime
+        self.w_router = fetch.matrix(s.prefix + "router")
+        self.correction = fetch.vector(s.prefix + "correction") if s.has_correction else None
+        if s.num_experts > 0:
+            # per expert: gate rows then up rows, so that one grouped product yields both
+            self.w_gate_up = torch.stack([torch.cat([fetch.matrix(f"{s.prefix}e{e}.gate"), fetch.matrix(f"{s.prefix}e{e}.up")], 0)
+                                          for e in range(s.num_experts)])
+            self.w_down = torch.stack([fetch.matrix(f"{s.prefix}e{e}.down") for e in range(s.num_experts)])
+            self.counts = torch.zeros(s.num_experts, dtype=torch.int32, device=runtime.device)
+        if s.shared_size > 0:
+            self.w_shared_gate_up = torch.cat([fetch.matrix(s.prefix + "shared.gate"), fetch.matrix(s.prefix + "shared.up")], 0)
+            self.w_shared_down = fetch.matrix(s.prefix + "shared.down")
+
+    def forward(self, x, ctx, residual) -> None:
+        s = self.spec
+        n, dev = x.shape[0], x.device
+        logits = linear(x, self.w_router, out_dtype=torch.float32)
+        ids = torch.empty((n, s.top_k), dtype=torch.int32, device=dev)
+        weights = torch.empty((n, s.top_k), dtype=torch.float32, device=dev)
+        ops.moe_route(logits, self.correction, ids, weights, n_groups=s.num_groups, keep=s.keep_groups)
+        table = ops.RoutingTable(n, s.top_k, max(s.num_experts, 1), dev)
+        expert_out = torch.empty((table.n_pairs, s.hidden_size), dtype=torch.float32, device=dev)
+        if s.num_experts > 0:
+            ops.moe_group(ids, self.counts, table)
+            act = torch.empty((table.n_pairs, s.expert_size), dtype=x.dtype, device=dev)
+            ops.grouped_gemm_routed(x, self.w_gate_up, act, table, gather=True, epi=ops.GROUPED_GATED_CLAMP,
+                                    limit=s.limit, alpha=s.gate_alpha)
+            ops.grouped_gemm_routed(act, self.w_down, expert_out, table, gather=False, epi=ops.GROUPED_STORE_F32)
+        ops.moe_combine(residual, expert_out, x, ids, weights, table)
+        if s.shared_size > 0:
+            act = torch.empty((n, s.shared_size), dtype=x.dtype, device=dev)
+            ops.gated_clamp(linear(x, self.w_shared_gate_up), act, s.shared_limit, s.gate_alpha)
+            linear(act, self.w_shared_down, residual=residual, track=ctx)
+
+
+register_part(RoutedExpertsSpec, RoutedExperts)

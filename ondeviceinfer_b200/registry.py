@@ -3,10 +3,11 @@
 An entry is a configuration class with three members: ``from_dict(raw)`` (typed
 configuration from the ``config.json`` dictionary), ``to_plan()`` (the
 :class:`~ondeviceinfer_b200.config.specs.ModelPlan` the engine builds) and
-``to_dict()`` (a ``config.json`` that reads back equal).  The reference has no
+``to_dict()`` (a ``config.json`` that reads back equal); optionally ``plan_for(stored)`` for a design that leaves
+some sizes to the shapes of the checkpoint's tensors.  The reference has no
 registry: it only checks ``model_type == "qwen3"`` (ondeviceinfer/config.py:40-43);
-here the model class is chosen by ``config.json["architectures"][0]``, with
-``model_type`` as the fallback for folders that lack that key.
+here the model class is chosen by ``config.json["architectures"][0]`` (or the single name
+under ``"architecture"``), with ``model_type`` as the fallback for folders that lack both.
 """
 
 from __future__ import annotations
@@ -37,6 +38,8 @@ def architecture_name(raw: Mapping[str, Any]) -> str:
     archs = raw.get("architectures") or []
     if archs:
         name = archs[0]
+    elif isinstance(raw.get("architecture"), str):
+        name = raw["architecture"]
     elif raw.get("model_type") in _MODEL_TYPES:
         name = _MODEL_TYPES[raw["model_type"]]
     else:
