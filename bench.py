@@ -581,6 +581,150 @@ def run_own_arm(args, parser) -> int:
     return 0
 
 
+# ------------------------------------------------------------------------------ another design beside the closest model
+
+def _lemesun_config(width, heads, dim, rot, vdim, rank, experts, identity, groups, keep, top, ff, shared_ff, layers, vocab):
+    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "shared": {"ff": shared_ff, "limit": 7.0},
+           "router": {"experts": experts, "identity": identity, "top": top, "groups": {"count": groups, "keep": keep}}}
+    latent = {"type": "latent_attention", "mlp": moe,
+              "mixer": {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank,
+                        "scale": (dim + rot) ** -0.5, "rot": {"base": 10000.0, "dims": rot}}}
+    delta = {"type": "channel_delta", "mlp": moe,
+             "mixer": {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": vdim, "conv": 4, "decay_rank": 64, "gate_rank": 64}}
+    return {"architecture": "Lemesun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [latent if i % 2 == 0 else delta for i in range(layers)]}
+
+
+def _dense_config(width, heads, intermediate, layers, vocab):
+    return dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=max(1, heads // 4), head_dim=128, intermediate_size=intermediate, vocab_size=vocab)
+
+
+# name -> (the design's configuration, the dense model of equal width and equal active feed-forward width)
+DESIGN_POINTS = {
+    "w2048": (_lemesun_config(2048, 16, 64, 32, 64, 256, 30, 2, 4, 2, 4, 1024, 1024, 4, 32768),
+              _dense_config(2048, 16, 5 * 1024, 4, 32768)),
+    "w4096": (_lemesun_config(4096, 32, 128, 64, 128, 512, 62, 2, 8, 4, 6, 1536, 3072, 4, 32768),
+              _dense_config(4096, 32, 6 * 1536 + 3072, 4, 32768)),
+}
+
+
+def _time_parts(model, cache, slots, runs, torch):
+    """Device time of every mixer and feed-forward call of one step, by part class: {name: [us, calls]}."""
+    events, restore = [], []
+    for block in model.decoder.layers:
+        for part in (block.mixer, block.ffn):
+            if part is None:
+                continue
+            original = part.forward
+
+            def timed(*a, _f=original, _n=type(part).__name__, **k):
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                out = _f(*a, **k)
+                end.record()
+                events.append((_n, start, end))
+                return out
+            part.forward = timed
+            restore.append((part, original))
+    try:
+        model.step(cache, slots, runs, "last")
+        torch.cuda.synchronize()
+    finally:
+        for part, original in restore:
+            part.forward = original
+    table = {}
+    for name, start, end in events:
+        entry = table.setdefault(name, [0.0, 0])
+        entry[0] += start.elapsed_time(end) * 1000.0
+        entry[1] += 1
+    return {name: {"us_per_call": round(total / calls, 1), "calls": calls} for name, (total, calls) in table.items()}
+
+
+def run_design_points(args) -> int:
+    """``--design lemesun``: prefill and decode throughput of the Lemesun design at layer sizes like a real model's
+    (random weights), each beside the dense Qwen3 model of equal width, heads and active feed-forward width, with
+    the device time of every mixer and feed-forward call.  One JSON line; the default workload is untouched."""
+    import torch
+
+    import ondeviceinfer_b200 as odi
+    from ondeviceinfer_b200.kernels import ops
+
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device is visible; this library has no CPU path")
+        return 2
+    peaks, peak_source = load_peaks()
+    prompt, batch, steps = args.prompt_len, args.batch, min(args.steps, 64)
+    gen = torch.Generator().manual_seed(args.seed)
+    points = {}
+    sampler = ClockSampler()
+    sampler.start()
+    for name, configs in DESIGN_POINTS.items():
+        if args.design_points and name not in args.design_points.split(","):
+            continue
+        for label, cfg in zip(("lemesun", "dense"), configs):
+            model = odi.random_resident_model(cfg, args.seed, dtype="bfloat16")
+            vocab = model.vocab_size
+            cache = model.make_cache(max_tokens=batch * (prompt + steps + 64 + 64), max_seqs=batch)
+            ids = torch.randint(0, vocab, (batch, prompt), generator=gen).tolist()
+            # prefill of one prompt: warm-up, then the median of three, each on an empty slot
+            times = []
+            for i in range(max(args.warmup, 3) + 3):
+                slot = cache.alloc()
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                start.record()
+                model.step(cache, [slot], [ids[0]], "last")
+                end.record()
+                torch.cuda.synchronize()
+                if i >= max(args.warmup, 3):
+                    times.append(start.elapsed_time(end))
+                cache.free(slot)
+            slot = cache.alloc()
+            prefill_parts = _time_parts(model, cache, [slot], [ids[0]], torch)
+            cache.free(slot)
+            prefill_ms = median(times)
+            # decode through generate(): the loop a user runs, graphs where the parts allow them
+            result = model.generate(ids, max_new_tokens=max(args.warmup, SETTLE_STEPS) + steps, cache=cache)
+            ops.raise_on_kernel_fault()
+            timed = result.step_seconds[-steps:]
+            step_ms = 1000.0 * median(timed)
+            slots = [cache.alloc() for _ in range(batch)]
+            model.step(cache, slots, ids, "last")
+            decode_parts = _time_parts(model, cache, slots, [[1]] * batch, torch)
+            weight_bytes = sum(t.numel() * t.element_size() for t in _tensors_of(model.decoder))
+            points.setdefault(name, {})[label] = {
+                "prefill_tokens_s": round(prompt / (prefill_ms / 1000.0), 1), "prefill_ms": round(prefill_ms, 3),
+                "decode_tokens_s": round(batch / (step_ms / 1000.0), 1), "decode_ms_per_step": round(step_ms, 3),
+                "graphs": bool(model.decoder.graph_safe), "weight_gb": round(weight_bytes / 1e9, 3),
+                "prefill_parts": prefill_parts, "decode_parts": decode_parts}
+            del model, cache
+            torch.cuda.empty_cache()
+    clocks = sampler.stop()
+    print(json.dumps({"metric": "prefill and decode tokens/s of the Lemesun design beside the dense model of equal size",
+                      "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "impl": "ours", "higher_is_better": True,
+                      "data": "synthetic: seeded random weights, uniform random token ids",
+                      "config": {"prompt_len": prompt, "global_batch": batch, "decode_steps": steps, "layers": 4,
+                                 "peaks": peak_source, "points": {k: {"lemesun": v[0], "dense": v[1]} for k, v in DESIGN_POINTS.items()
+                                                                  if k in points}},
+                      "peaks": peaks, "points": points, "clocks": clocks}))
+    return 0
+
+
+def _tensors_of(decoder):
+    seen, out = set(), []
+    stack = [decoder.embedding, decoder.final_norm, decoder.head, *decoder.layers]
+    while stack:
+        part = stack.pop()
+        for value in vars(part).values():
+            if hasattr(value, "data_ptr") and hasattr(value, "numel") and value.data_ptr() not in seen:
+                seen.add(value.data_ptr())
+                out.append(value)
+            elif hasattr(value, "tensor_decls"):
+                stack.append(value)
+    return out
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -599,12 +743,17 @@ def main() -> int:
     parser.add_argument("--prompt-range", default=None, metavar="LOW,HIGH",
                         help="unequal prompts: lengths uniform in [LOW, HIGH] from --seed instead of --prompt-len")
     parser.add_argument("--context", type=int, default=None, help="cache positions per sequence (default 4096, or what the prompt needs)")
+    parser.add_argument("--design", default=None, choices=["lemesun"],
+                        help="instead of the default workload: this design at real layer sizes beside the dense model of equal size")
+    parser.add_argument("--design-points", default=None, help="which of the design's sizes, with commas (default: all)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported (use --gpus 1)")
         return 2
     if args.impl == "reference":
         return run_reference_arm(args, parser)
+    if args.design is not None:
+        return run_design_points(args)
     return run_own_arm(args, parser)
 
 

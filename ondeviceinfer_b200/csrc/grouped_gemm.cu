@@ -12,12 +12,11 @@
 // Epilogues: 0 store as T, 1 store as fp32, 2 gated and clamped (W_g holds N gate rows then N up rows;
 // g = min(gate, limit), u = clamp(up, -limit, limit), C = g * sigmoid(alpha * g) * (u + 1) as T).
 //
-// Tile: TM rows x 64 features per block of 256 threads, K in slices of 16 through shared memory (fp32).
+// Tile: TM rows x 64 features per block of 256 threads, K in slices of 16 or 32 through shared memory (fp32).
 // TM = 64 (4 x 4 outputs a thread) or 16 (1 x 4), chosen by the caller from the rows a group has.
 #include "common.cuh"
 
 #define TN 64
-#define TK 16
 
 struct GroupedArgs {
   const void* A;
@@ -33,14 +32,35 @@ struct GroupedArgs {
   float limit, alpha;
 };
 
-template <typename T, int TM, bool GATED>
+// Eight consecutive elements of a row as floats (16-byte loads; the caller has checked the alignment).
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* out);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* out) {
+  const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+  out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float* out) {
+  const uint4 raw = *(const uint4*)p;
+  const __nv_bfloat162* h = (const __nv_bfloat162*)&raw;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); out[2 * i] = f.x; out[2 * i + 1] = f.y; }
+}
+
+// A k-major tile in shared memory, [TK][STR] floats with 8 more floats after every 8 k: the four 8-element
+// pieces of a row's 32 k land in different banks when one warp stores them.
+#define SIDX(k, i, STR) ((k) * (STR) + ((k) >> 3) * 8 + (i))
+
+// VEC: K, the row strides and the group offsets are multiples of 8 elements and the bases 16-byte aligned:
+// slices of 32 k, one 8-element piece per thread and tile; else slices of 16 k, element by element.
+template <typename T, int TM, bool GATED, bool VEC>
 __global__ void __launch_bounds__(256)
 grouped_gemm_kernel(GroupedArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int RPT = TM / 16;
-  __shared__ __align__(16) float As[TK][TM + 4];
-  __shared__ __align__(16) float Ws[GATED ? 2 : 1][TK][TN + 4];
+  constexpr int TK = VEC ? 32 : 16;
+  constexpr int ASTR = TM + 4, WSTR = TN + 4;
+  __shared__ __align__(16) float As[TK * ASTR + (TK / 8) * 8];
+  __shared__ __align__(16) float Ws[GATED ? 2 : 1][TK * WSTR + (TK / 8) * 8];
   __shared__ int arow[TM];
   const int tid = threadIdx.x;
   int group, row0, rows;
@@ -65,26 +85,53 @@ grouped_gemm_kernel(GroupedArgs a) {
 
   for (int k0 = 0; k0 < a.K; k0 += TK) {
     __syncthreads();
-    for (int i = tid; i < TM * TK; i += 256) {
-      const int r = i / TK, k = i % TK;
-      const int src = arow[r];
-      As[k][r] = (src >= 0 && k0 + k < a.K) ? to_f<T>(A[(size_t)src * a.lda + k0 + k]) : 0.f;
-    }
-    for (int i = tid; i < TN * TK; i += 256) {
-      const int n = i / TK, k = i % TK;
-      const bool in = n0 + n < a.N && k0 + k < a.K;
-      Ws[0][k][n] = in ? to_f<T>(W[(size_t)(n0 + n) * a.ldw + k0 + k]) : 0.f;
-      if (GATED) Ws[1][k][n] = in ? to_f<T>(W[(size_t)(a.N + n0 + n) * a.ldw + k0 + k]) : 0.f;
+    if (VEC) {
+      const int piece = tid & 3, k = k0 + piece * 8;     // four pieces of 8 k per row
+      float v[8];
+      if (tid < TM * 4) {
+        const int r = tid >> 2, src = arow[r];
+        if (src >= 0 && k < a.K) load8<T>(A + (size_t)src * a.lda + k, v);
+        else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) As[SIDX(piece * 8 + i, r, ASTR)] = v[i];
+      }
+      const int n = tid >> 2;
+      const bool in = n0 + n < a.N && k < a.K;
+#pragma unroll
+      for (int s = 0; s < (GATED ? 2 : 1); ++s) {
+        if (in) load8<T>(W + (size_t)(s * a.N + n0 + n) * a.ldw + k, v);
+        else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) Ws[s][SIDX(piece * 8 + i, n, WSTR)] = v[i];
+      }
+    } else {
+      for (int i = tid; i < TM * TK; i += 256) {
+        const int r = i / TK, k = i % TK;
+        const int src = arow[r];
+        As[SIDX(k, r, ASTR)] = (src >= 0 && k0 + k < a.K) ? to_f<T>(A[(size_t)src * a.lda + k0 + k]) : 0.f;
+      }
+      for (int i = tid; i < TN * TK; i += 256) {
+        const int n = i / TK, k = i % TK;
+        const bool in = n0 + n < a.N && k0 + k < a.K;
+        Ws[0][SIDX(k, n, WSTR)] = in ? to_f<T>(W[(size_t)(n0 + n) * a.ldw + k0 + k]) : 0.f;
+        if (GATED) Ws[1][SIDX(k, n, WSTR)] = in ? to_f<T>(W[(size_t)(a.N + n0 + n) * a.ldw + k0 + k]) : 0.f;
+      }
     }
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < TK; ++k) {
       float ar[RPT];
 #pragma unroll
-      for (int i = 0; i < RPT; ++i) ar[i] = As[k][ty * RPT + i];
+      for (int i = 0; i < RPT; ++i) ar[i] = As[SIDX(k, ty * RPT + i, ASTR)];
 #pragma unroll
       for (int s = 0; s < (GATED ? 2 : 1); ++s) {
-        const float4 wv = *(const float4*)&Ws[s][k][tx * 4];
+        const float4 wv = *(const float4*)&Ws[s][SIDX(k, tx * 4, WSTR)];
         const float wr[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
         for (int i = 0; i < RPT; ++i)
@@ -131,7 +178,13 @@ extern "C" int odi_grouped_gemm(const GroupedArgs* args, int max_tiles, int tm, 
     if (grid.z > 65535) return ODI_ERR_UNSUPPORTED;
   }
   if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
-#define ODI_GG(T, TM, G) odi_rc = launch_pdl((grouped_gemm_kernel<T, TM, G>), grid, dim3(256), 0, stream, a)
+  const size_t elem = dtype == 0 ? 4 : 2;
+  const bool vec = a.K % 8 == 0 && a.lda % 8 == 0 && a.ldw % 8 == 0 && a.a_group_off % 8 == 0 &&
+                   a.w_group_stride % 8 == 0 && (uintptr_t)a.A % 16 == 0 && (uintptr_t)a.W % 16 == 0 &&
+                   ((size_t)a.N * a.ldw * elem) % 16 == 0;
+#define ODI_GG(T, TM, G) \
+  do { if (vec) odi_rc = launch_pdl((grouped_gemm_kernel<T, TM, G, true>), grid, dim3(256), 0, stream, a); \
+       else odi_rc = launch_pdl((grouped_gemm_kernel<T, TM, G, false>), grid, dim3(256), 0, stream, a); } while (0)
   const bool gated = a.epi == 2;
   if (dtype == 0) {
     if (tm == 64) { if (gated) ODI_GG(float, 64, true); else ODI_GG(float, 64, false); }

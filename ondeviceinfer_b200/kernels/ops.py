@@ -1106,6 +1106,8 @@ def delta_rule(proj: torch.Tensor, decay_in: torch.Tensor, taps: torch.Tensor, a
 
 # ------------------------------------------------------------------------------ sampling
 
+_sample_state = {}
+
 
 def _sample_buffers(device, rows: int, chunks: int):
     """Per-chunk partial results (16 bytes each) and one ticket per row (kept zero between launches)."""

@@ -158,3 +158,117 @@ def forward(cfg, w, ids, keep_layers=False):
         after.append(x)
     logits = offset_norm(x, w["final.norm"], eps) @ w["head"].T
     return (logits, torch.stack(after)) if keep_layers else logits
+
+
+# ----------------------------------------------------------------------------- small configurations and weights
+
+
+def latent_layer(heads, dim, rot_dim, vdim, kv_rank, scale, base, mlp, **more):
+    return {"type": "latent_attention", "mlp": mlp, **more,
+            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "scale": scale,
+                      "rot": {"base": base, "dims": rot_dim}}}
+
+
+def delta_layer(heads, kv_heads, dim, vdim, conv, mlp, **more):
+    return {"type": "channel_delta", "mlp": mlp, **more,
+            "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}}
+
+
+def moe(experts, identity, top, groups, keep, ff, limit, shared=None):
+    return {"kind": "moe", "expert": {"ff": ff, "limit": limit},
+            "router": {"experts": experts, "identity": identity, "top": top, "groups": {"count": groups, "keep": keep}},
+            "shared": shared}
+
+
+def model_config(vocab, width, eps, layers):
+    return {"architecture": "Lemesun", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+
+
+_MOE_A = moe(6, 2, 3, 4, 2, 24, 1.0, {"ff": 40, "limit": 0.7})
+_MOE_B = moe(3, 0, 1, 1, 1, 20, 2.5)
+# A: both mixers, a layer run twice, a layer without feed-forward, identity outputs, groups, a shared expert,
+#    grouped q/k heads, a value size beyond one block of columns
+TINY_A = model_config(97, 48, 1e-5, [
+    latent_layer(3, 8, 4, 12, 20, 0.3, 100.0, _MOE_A),
+    delta_layer(4, 2, 16, 8, 3, _MOE_A),
+    latent_layer(3, 8, 4, 12, 20, 0.3, 100.0, _MOE_A, weights_of=0),
+    delta_layer(2, 2, 40, 36, 2, None),
+    delta_layer(4, 2, 16, 8, 3, _MOE_A, weights_of=1)])
+# B: sizes of one (one head, one tap, one group, top 1), no identity outputs, no shared expert, delta first
+TINY_B = model_config(61, 64, 1e-6, [
+    delta_layer(1, 1, 24, 16, 1, _MOE_B),
+    latent_layer(1, 16, 8, 16, 24, 0.2, 5000.0, _MOE_B),
+    delta_layer(3, 3, 72, 16, 4, _MOE_B)])
+# one mixer alone, no feed-forward
+ONLY_LATENT = model_config(53, 32, 1e-6, [latent_layer(4, 8, 8, 8, 16, 0.35, 1000.0, None)])
+ONLY_DELTA = model_config(53, 32, 1e-6, [delta_layer(4, 2, 16, 12, 4, None)])
+BOTTLENECKS = (6, 10)     # widths of the decay and gate bottlenecks in every test model
+
+
+def random_weights(cfg, seed, sharpen=1.0):
+    """bfloat16 tensors under the checkpoint names; scales chosen so that every mechanism moves the logits.
+    ``sharpen`` multiplies the query projections of latent attention (peaky softmax: a lost key shows)."""
+    g = torch.Generator().manual_seed(seed)
+    W = cfg["width"]
+
+    def mat(rows, cols, scale=1.0):
+        return (torch.randn(rows, cols, generator=g) * scale / cols ** 0.5).to(torch.bfloat16)
+
+    def vec(n, scale, shift=0.0):
+        return (torch.randn(n, generator=g) * scale + shift).to(torch.bfloat16)
+
+    w = {"embed": (torch.randn(cfg["vocab"], W, generator=g)).to(torch.bfloat16), "final.norm": vec(W, 0.1),
+         "head": mat(cfg["vocab"], W)}
+    for i, layer in enumerate(cfg["layers"]):
+        if layer.get("weights_of") is not None:
+            continue
+        p, m = f"l{i}.", layer["mixer"]
+        w[p + "norm1"] = vec(W, 0.1)
+        if layer["type"] == "latent_attention":
+            H, d, r, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            w[p + "mix.q"] = mat(H * (d + r), W, 2.0 * sharpen)
+            w[p + "mix.dkv"] = mat(R + r, W, 2.0)
+            w[p + "mix.dkv.norm"] = vec(R, 0.2, 1.0)
+            w[p + "mix.uk"] = mat(H * d, R, 2.0)
+            w[p + "mix.uv"] = mat(H * dv, R)
+            w[p + "mix.o"] = mat(W, H * dv)
+        else:
+            H, G, d, dv, K = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+            ra, rg = BOTTLENECKS
+            for name, rows in (("q", G * d), ("k", G * d), ("v", H * dv)):
+                w[p + f"mix.{name}"] = mat(rows, W, 2.0)
+                w[p + f"mix.{name}.conv"] = (torch.randn(rows, K, generator=g) * 0.6).to(torch.bfloat16)
+            w[p + "mix.b"] = mat(H, W, 2.0)
+            w[p + "mix.A_log"] = vec(H, 0.5, -1.0)
+            w[p + "mix.norm"] = vec(dv, 0.2, 1.0)
+            w[p + "mix.a1"] = mat(ra, W)
+            w[p + "mix.a2"] = mat(H * d, ra, 2.0)
+            w[p + "mix.dt_bias"] = vec(H * d, 1.0)
+            w[p + "mix.g1"] = mat(rg, W)
+            w[p + "mix.g2"] = mat(H * dv, rg, 2.0)
+            w[p + "mix.o"] = mat(W, H * dv)
+        f = layer.get("mlp")
+        if f is None:
+            continue
+        w[p + "norm2"] = vec(W, 0.1)
+        n_all = f["router"]["experts"] + f["router"]["identity"]
+        w[p + "mlp.router"] = mat(n_all, W, 3.0)
+        w[p + "mlp.correction"] = vec(n_all, 0.05)
+        for e in range(f["router"]["experts"]):
+            w[p + f"mlp.e{e}.gate"] = mat(f["expert"]["ff"], W, 2.0)
+            w[p + f"mlp.e{e}.up"] = mat(f["expert"]["ff"], W, 2.0)
+            w[p + f"mlp.e{e}.down"] = mat(W, f["expert"]["ff"], 2.0)
+        if f.get("shared"):
+            w[p + "mlp.shared.gate"] = mat(f["shared"]["ff"], W, 2.0)
+            w[p + "mlp.shared.up"] = mat(f["shared"]["ff"], W, 2.0)
+            w[p + "mlp.shared.down"] = mat(W, f["shared"]["ff"])
+    return w
+
+
+def random_prompts(cfg, lengths, seed):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in lengths]
+
+
+def widened(weights, dtype=torch.float64):
+    return {k: v.to(dtype) for k, v in weights.items()}
