@@ -28,6 +28,8 @@ struct LatentPrepArgs {
   const int* page_ids;
   int n_tokens, ld, heads, d, r, R, rot_dims, interleaved, page_size, ring_pages, write_cache;
   float eps;
+  void* latent_out;      // null, or [n_tokens, R] in T: the normed latent once more, rows side by side
+  void* key_rot_out;     // null, or [n_tokens, r] in T: the rotated shared key lanes once more
 };
 
 __device__ __forceinline__ void rotated_pair(int lane, int rot_dims, int interleaved, int* a, int* b, int* i) {
@@ -72,11 +74,71 @@ latent_prep_kernel(LatentPrepArgs a) {
     for (int i = threadIdx.x; i < a.R; i += blockDim.x) dst[i] = from_f<T>(to_f<T>(down[i]) * inv * a.norm_w[i]);
     for (int i = threadIdx.x; i < a.r; i += blockDim.x) dst[a.R + i] = from_f<T>(rotate_lane<T>(down + a.R, i, a, cs, sn));
   }
+  if (a.latent_out != nullptr) {
+    T* lat = (T*)a.latent_out + (size_t)t * a.R;
+    T* kr = (T*)a.key_rot_out + (size_t)t * a.r;
+    for (int i = threadIdx.x; i < a.R; i += blockDim.x) lat[i] = from_f<T>(to_f<T>(down[i]) * inv * a.norm_w[i]);
+    for (int i = threadIdx.x; i < a.r; i += blockDim.x) kr[i] = from_f<T>(rotate_lane<T>(down + a.R, i, a, cs, sn));
+  }
   T* q_out = (T*)a.q_abs + (size_t)t * a.heads * W;
   for (int i = threadIdx.x; i < a.heads * a.r; i += blockDim.x) {
     const int h = i / a.r, lane = i % a.r;
     q_out[(size_t)h * W + a.R + lane] = from_f<T>(rotate_lane<T>(row + h * (a.d + a.r) + a.d, lane, a, cs, sn));
   }
+}
+
+// Whole heads for a prompt that starts its sequence: the attention kernels for ordinary heads then serve it.
+// Per (token, head): query [plain lanes | rotated lanes | zeros] into q_full [tokens, heads, Dh]; key
+// [up-projected plain lanes | the shared rotated lanes | zeros] and value [up-projected lanes | zeros] into
+// pools [pages, heads, page_size, Dh] of the step's own, where sequence s holds pages page_start[s].. in order.
+struct LatentExpandArgs {
+  const void* proj;      // [n_tokens, ld]: per head d plain query lanes (then r lanes that are not read here)
+  const void* q_abs;     // [n_tokens, heads, R + r]: the rotated query lanes at R..
+  const void* k_plain;   // [n_tokens, heads * d]
+  const void* key_rot;   // [n_tokens, r]
+  const void* v;         // [n_tokens, heads * dv]
+  void* q_full;
+  void* k_pool;
+  void* v_pool;
+  const int* tok_seq;
+  const int* cu_q;
+  const int* page_start;
+  int n_tokens, ld, heads, d, r, R, dv, Dh, page_size;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_expand_kernel(LatentExpandArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int seq = a.tok_seq[t];
+  const int li = t - a.cu_q[seq];
+  const size_t slot = ((size_t)(a.page_start[seq] + li / a.page_size) * a.heads + h) * a.page_size + li % a.page_size;
+  const T* qp = (const T*)a.proj + (size_t)t * a.ld + h * (a.d + a.r);
+  const T* qr = (const T*)a.q_abs + ((size_t)t * a.heads + h) * (a.R + a.r) + a.R;
+  const T* kp = (const T*)a.k_plain + ((size_t)t * a.heads + h) * a.d;
+  const T* kr = (const T*)a.key_rot + (size_t)t * a.r;
+  const T* vp = (const T*)a.v + ((size_t)t * a.heads + h) * a.dv;
+  T* q = (T*)a.q_full + ((size_t)t * a.heads + h) * a.Dh;
+  T* k = (T*)a.k_pool + slot * a.Dh;
+  T* v = (T*)a.v_pool + slot * a.Dh;
+  const T zero = from_f<T>(0.f);
+  for (int i = threadIdx.x; i < a.Dh; i += blockDim.x) {
+    q[i] = i < a.d ? qp[i] : (i < a.d + a.r ? qr[i - a.d] : zero);
+    k[i] = i < a.d ? kp[i] : (i < a.d + a.r ? kr[i - a.d] : zero);
+    v[i] = i < a.dv ? vp[i] : zero;
+  }
+}
+
+extern "C" int odi_latent_expand(const LatentExpandArgs* args, int dtype, cudaStream_t stream) {
+  const LatentExpandArgs a = *args;
+  if (a.n_tokens <= 0) return 0;
+  if (a.Dh < a.d + a.r || a.Dh < a.dv || a.heads <= 0 || a.heads > 65535) return ODI_ERR_ARGUMENT;
+  const dim3 grid(a.n_tokens, a.heads);
+  if (dtype == 0) odi_rc = launch_pdl((latent_expand_kernel<float>), grid, dim3(128), 0, stream, a);
+  else odi_rc = launch_pdl((latent_expand_kernel<bf16>), grid, dim3(128), 0, stream, a);
+  return launch_status();
 }
 
 extern "C" int odi_latent_prep(const LatentPrepArgs* args, int dtype, cudaStream_t stream) {

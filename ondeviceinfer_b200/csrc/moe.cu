@@ -10,6 +10,7 @@
 //  scatter  per pair: its place in the sorted order (`pos`) and the order itself (`perm`).
 //  combine  per token: residual += sum over its choices, in the order of the choices, of weight times the
 //           expert's output row -- or times the token's own input for an identity output (index >= n_experts).
+//  gather   the routed tokens' input rows in the sorted order (for products that want their rows side by side).
 //  gated_clamp  the experts' activation on a [tokens, 2 F] product (gate lanes, then up lanes):
 //           g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1).
 #include "common.cuh"
@@ -206,6 +207,27 @@ extern "C" int odi_moe_combine(const CombineArgs* args, int dtype, cudaStream_t 
   const int threads = a.H >= 1024 ? 256 : 128;
   if (dtype == 0) odi_rc = launch_pdl((moe_combine_kernel<float>), dim3(a.n_tokens), dim3(threads), 0, stream, a);
   else odi_rc = launch_pdl((moe_combine_kernel<bf16>), dim3(a.n_tokens), dim3(threads), 0, stream, a);
+  return launch_status();
+}
+
+// Rows of the routed tokens' inputs in the sorted order: out[i] = x[perm[i] / top] for the places that are taken.
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ perm, const int* __restrict__ offsets,
+                                  T* __restrict__ out, int H, int top, int n_experts) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x;
+  if (i >= offsets[n_experts]) return;
+  const T* src = x + (size_t)(perm[i] / top) * H;
+  T* dst = out + (size_t)i * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = src[c];
+}
+
+extern "C" int odi_moe_gather(const void* x, const int* perm, const int* offsets, void* out, int n_pairs, int H, int top,
+                              int n_experts, int dtype, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (dtype == 0) odi_rc = launch_pdl((moe_gather_kernel<float>), dim3(n_pairs), dim3(128), 0, stream, (const float*)x, perm, offsets, (float*)out, H, top, n_experts);
+  else odi_rc = launch_pdl((moe_gather_kernel<bf16>), dim3(n_pairs), dim3(128), 0, stream, (const bf16*)x, perm, offsets, (bf16*)out, H, top, n_experts);
   return launch_status();
 }
 

@@ -881,12 +881,13 @@ class _LatentPrepArgs(Structure):
                 ("page_start", c_void_p), ("page_ids", c_void_p),
                 ("n_tokens", c_int), ("ld", c_int), ("heads", c_int), ("d", c_int), ("r", c_int), ("R", c_int),
                 ("rot_dims", c_int), ("interleaved", c_int), ("page_size", c_int), ("ring_pages", c_int),
-                ("write_cache", c_int), ("eps", c_float)]
+                ("write_cache", c_int), ("eps", c_float), ("latent_out", c_void_p), ("key_rot_out", c_void_p)]
 
 
 def latent_prep(proj: torch.Tensor, q_abs: torch.Tensor, pool: torch.Tensor, norm_w: torch.Tensor, cos_t, sin_t,
                 tok_seq, tok_pos, page_start, page_ids, *, heads: int, d: int, r: int, R: int, rot_dims: int,
-                interleaved: bool, page_size: int, ring_pages: int, write_cache: bool, eps: float) -> None:
+                interleaved: bool, page_size: int, ring_pages: int, write_cache: bool, eps: float,
+                latent_out: Optional[torch.Tensor] = None, key_rot_out: Optional[torch.Tensor] = None) -> None:
     """From the fused query / down projection ``proj`` [tokens, heads (d + r) + R + r]: the normed latent and the
     rotated shared key lanes into the token's cache row, each head's rotated query lanes into lanes R.. of
     ``q_abs`` [tokens, heads, R + r] (see ``csrc/latent.cu``)."""
@@ -902,11 +903,46 @@ def latent_prep(proj: torch.Tensor, q_abs: torch.Tensor, pool: torch.Tensor, nor
         _require(sin_t, "sin_t", torch.float32, 2)
         if cos_t.shape != (n, rot_dims // 2) or sin_t.shape != cos_t.shape:
             raise KernelError("rotary tables do not fit the tokens")
+    if (latent_out is None) != (key_rot_out is None):
+        raise KernelError("latent_out and key_rot_out go together")
+    if latent_out is not None:
+        _require(latent_out, "latent_out", proj.dtype, 2)
+        _require(key_rot_out, "key_rot_out", proj.dtype, 2)
+        if latent_out.shape != (n, R) or key_rot_out.shape != (n, r):
+            raise KernelError("latent_out is [tokens, R] and key_rot_out [tokens, r]")
     args = _LatentPrepArgs(_ptr(proj), _ptr(q_abs), _ptr(pool), _ptr(norm_w), _ptr(cos_t), _ptr(sin_t), _ptr(tok_seq),
                            _ptr(tok_pos), _ptr(page_start), _ptr(page_ids), n, proj.shape[1], heads, d, r, R, rot_dims,
-                           1 if interleaved else 0, page_size, ring_pages, 1 if write_cache else 0, eps)
+                           1 if interleaved else 0, page_size, ring_pages, 1 if write_cache else 0, eps,
+                           _ptr(latent_out), _ptr(key_rot_out))
     lib = load_library("latent")
     _check(lib.odi_latent_prep(byref(args), c_int(dtype_code(proj.dtype)), _stream()), "latent_prep")
+
+
+class _LatentExpandArgs(Structure):
+    _fields_ = [("proj", c_void_p), ("q_abs", c_void_p), ("k_plain", c_void_p), ("key_rot", c_void_p), ("v", c_void_p),
+                ("q_full", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p), ("tok_seq", c_void_p),
+                ("cu_q", c_void_p), ("page_start", c_void_p),
+                ("n_tokens", c_int), ("ld", c_int), ("heads", c_int), ("d", c_int), ("r", c_int), ("R", c_int),
+                ("dv", c_int), ("Dh", c_int), ("page_size", c_int)]
+
+
+def latent_expand(proj, q_abs, k_plain, key_rot, v, q_full, k_pool, v_pool, tok_seq, cu_q, page_start, *, heads: int,
+                  d: int, r: int, R: int, dv: int, Dh: int, page_size: int) -> None:
+    """Whole heads of ``Dh`` lanes for prompts that start their sequences (``csrc/latent.cu``): queries into ``q_full``
+    [tokens, heads, Dh], keys and values into pools [pages, heads, page_size, Dh] where sequence s holds the pages
+    from ``page_start[s]`` on, in order."""
+    n = proj.shape[0]
+    for name, t in (("proj", proj), ("q_abs", q_abs), ("k_plain", k_plain), ("key_rot", key_rot), ("v", v),
+                    ("q_full", q_full), ("k_pool", k_pool), ("v_pool", v_pool)):
+        _require(t, name, proj.dtype)
+    if (k_plain.shape != (n, heads * d) or v.shape != (n, heads * dv) or key_rot.shape != (n, r)
+            or q_full.numel() != n * heads * Dh or k_pool.shape[1:] != (heads, page_size, Dh) or v_pool.shape != k_pool.shape):
+        raise KernelError("latent_expand sizes disagree")
+    args = _LatentExpandArgs(_ptr(proj), _ptr(q_abs), _ptr(k_plain), _ptr(key_rot), _ptr(v), _ptr(q_full), _ptr(k_pool),
+                             _ptr(v_pool), _ptr(tok_seq), _ptr(cu_q), _ptr(page_start), n, proj.shape[1], heads, d, r, R,
+                             dv, Dh, page_size)
+    lib = load_library("latent")
+    _check(lib.odi_latent_expand(byref(args), c_int(dtype_code(proj.dtype)), _stream()), "latent_expand")
 
 
 # ------------------------------------------------------------------------------ grouped products and routing
@@ -1024,6 +1060,18 @@ def moe_group(ids: torch.Tensor, counts: torch.Tensor, table: RoutingTable) -> N
                          _ptr(table.n_tiles), table.n_pairs, table.n_experts, table.tm, table.max_tiles)
     lib = load_library("moe")
     _check(lib.odi_moe_group(byref(args), _stream()), "moe_group", 3)
+
+
+def moe_gather(x: torch.Tensor, table: RoutingTable, out: torch.Tensor) -> None:
+    """out[i] = x[perm[i] // top] for every taken place i of ``table``'s sorted order (other rows are left alone)."""
+    _require(x, "x", ndim=2)
+    _require(out, "out", x.dtype, 2)
+    if out.shape != (table.n_pairs, x.shape[1]):
+        raise KernelError("moe_gather sizes disagree")
+    lib = load_library("moe")
+    _check(lib.odi_moe_gather(_ptr(x), _ptr(table.perm), _ptr(table.offsets), _ptr(out), c_int(table.n_pairs),
+                              c_int(x.shape[1]), c_int(table.top), c_int(table.n_experts), c_int(dtype_code(x.dtype)),
+                              _stream()), "moe_gather")
 
 
 class _CombineArgs(Structure):

@@ -14,6 +14,12 @@ up-projection is applied to the attention's output.  Steps of ``forward``:
    for single-token steps;
 5. a product per head with ``W_uv``, then the output projection with the residual add.
 
+A bfloat16 step whose sequences all start (prompts) takes the other way round instead, because whole heads are
+what the tensor-core attention kernels take: keys and values are up-projected for the step's tokens (two
+products), laid out as heads of ``head_lanes`` lanes in pages of the step's own (``latent_expand``), and the
+prefill kernels for ordinary heads run on them; the output projection reads those padded heads through a copy
+of its weight with zero columns for the padding.  The cache still receives only the latent rows.
+
 Scores, softmax, the latent norm and the angles are fp32 in both compute dtypes.
 """
 
@@ -27,6 +33,9 @@ from ..kernels import ops
 from ..weights.tensors import TensorDecl
 from .base import Part, build_part, register_part
 from .linear import linear
+
+WHOLE_HEADS_MIN_TOKENS = 32      # shorter prompts stay with the kernel over the latent rows
+WHOLE_HEADS_MAX_LANES = 256      # the widest head of the tensor-core prefill kernels
 
 
 class LatentAttention(Part):
@@ -44,6 +53,8 @@ class LatentAttention(Part):
         if self.position.rot_dim > spec.rot_dim:
             raise ValueError("the position encoding rotates more lanes than the heads have rotated lanes")
         self.row = spec.kv_rank + spec.rot_dim        # width of a cache row and of an absorbed query
+        # lanes of a whole head (query/key: plain + rotated; value), in the steps of 16 the prefill kernels take
+        self.head_lanes = -(-max(spec.qk_dim + spec.rot_dim, spec.v_dim) // 16) * 16
 
     def tensor_decls(self):
         s = self.spec
@@ -64,6 +75,13 @@ class LatentAttention(Part):
         self.w_uk_t = fetch.matrix(s.name("uk")).view(s.num_heads, s.qk_dim, s.kv_rank).transpose(1, 2).contiguous()
         self.w_uv = fetch.matrix(s.name("uv")).view(s.num_heads, s.v_dim, s.kv_rank).contiguous()
         self.w_o = fetch.matrix(s.name("o"))
+        self.w_uk = self.w_uv_rows = self.w_o_padded = None
+        if runtime.dtype == torch.bfloat16 and self.head_lanes <= WHOLE_HEADS_MAX_LANES:
+            self.w_uk = fetch.matrix(s.name("uk"))
+            self.w_uv_rows = self.w_uv.view(s.num_heads * s.v_dim, s.kv_rank)
+            padded = torch.zeros((s.hidden_size, s.num_heads, self.head_lanes), dtype=self.w_o.dtype, device=self.w_o.device)
+            padded[:, :, :s.v_dim] = self.w_o.view(s.hidden_size, s.num_heads, s.v_dim)
+            self.w_o_padded = padded.view(s.hidden_size, s.num_heads * self.head_lanes)
         self.position.load(fetch, runtime)
 
     def cache_needs(self):
@@ -78,11 +96,19 @@ class LatentAttention(Part):
         tables = self.position.rotary_tables(ctx)
         cos, sin = tables if tables is not None else (None, None)
         q_abs = torch.empty((n, s.num_heads * self.row), dtype=proj.dtype, device=proj.device)
+        whole_heads = (self.w_o_padded is not None and ctx.max_q_len >= WHOLE_HEADS_MIN_TOKENS
+                       and not any(ctx.past_lens) and not torch.cuda.is_current_stream_capturing())
+        latent = torch.empty((n, s.kv_rank), dtype=proj.dtype, device=proj.device) if whole_heads else None
+        key_rot = torch.empty((n, s.rot_dim), dtype=proj.dtype, device=proj.device) if whole_heads else None
         ops.latent_prep(proj, q_abs, view.keys, self.latent_norm, cos, sin, ctx.tok_seq, ctx.tok_pos, page_start,
                         page_ids, heads=s.num_heads, d=s.qk_dim, r=s.rot_dim, R=s.kv_rank,
                         rot_dims=self.position.rot_dim if cos is not None else 0,
                         interleaved=getattr(self.position, "interleaved", False), page_size=PAGE_SIZE,
-                        ring_pages=group.ring_pages, write_cache=view.writes_kv, eps=s.norm_eps)
+                        ring_pages=group.ring_pages, write_cache=view.writes_kv, eps=s.norm_eps,
+                        latent_out=latent, key_rot_out=key_rot)
+        if whole_heads:
+            self._attend_whole_heads(proj, q_abs, latent, key_rot, ctx, residual)
+            return
         ops.grouped_gemm_heads(proj, self.w_uk_t, q_abs, a_col=0, a_stride=s.qk_dim + s.rot_dim, c_col=0,
                                c_stride=self.row, K=s.qk_dim)
         latent_out = self.attend(q_abs, ctx, view, page_start, page_ids)
@@ -90,6 +116,37 @@ class LatentAttention(Part):
         ops.grouped_gemm_heads(latent_out, self.w_uv, heads_out, a_col=0, a_stride=s.kv_rank, c_col=0,
                                c_stride=s.v_dim, K=s.kv_rank)
         linear(heads_out, self.w_o, residual=residual, track=ctx)
+
+    def _attend_whole_heads(self, proj, q_abs, latent, key_rot, ctx, residual) -> None:
+        """Prompts from their first token on: attention over up-projected heads in pages of the step's own."""
+        s, n, lanes, dev = self.spec, proj.shape[0], self.head_lanes, proj.device
+
+        def pages_of_the_step():
+            counts = [-(-t // PAGE_SIZE) for t in ctx.q_lens]
+            starts = [0]
+            for c in counts:
+                starts.append(starts[-1] + c)
+            table = torch.tensor(starts + list(range(starts[-1])) + [0] * ctx.n_seqs, dtype=torch.int32).to(dev)
+            return (table[:ctx.n_seqs + 1], table[ctx.n_seqs + 1:ctx.n_seqs + 1 + starts[-1]],
+                    table[ctx.n_seqs + 1 + starts[-1]:], starts[-1])
+
+        page_start, page_ids, no_past, n_pages = ctx.memo("pages of a step whose sequences all start", pages_of_the_step)
+        k_plain = linear(latent, self.w_uk)
+        values = linear(latent, self.w_uv_rows)
+        # zeros: a page's rows beyond its sequence's end are multiplied by weights of zero
+        pools = torch.zeros((2, n_pages, s.num_heads, PAGE_SIZE, lanes), dtype=proj.dtype, device=dev)
+        q_full = torch.empty((n, s.num_heads * lanes), dtype=proj.dtype, device=dev)
+        ops.latent_expand(proj, q_abs, k_plain, key_rot, values, q_full, pools[0], pools[1], ctx.tok_seq, ctx.cu_q,
+                          page_start, heads=s.num_heads, d=s.qk_dim, r=s.rot_dim, R=s.kv_rank, dv=s.v_dim, Dh=lanes,
+                          page_size=PAGE_SIZE)
+        out = torch.empty_like(q_full)
+        sizes = dict(n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_heads, d=lanes,
+                     page_size=PAGE_SIZE, scale=s.scale)
+        if lanes in ops.TCGEN05_ATTENTION_HEAD_DIMS:
+            ops.attention_tcgen05(q_full, pools[0], pools[1], out, ctx.cu_q, no_past, page_start, page_ids, **sizes)
+        else:
+            ops.attention_mma(q_full, pools[0], pools[1], out, ctx.cu_q, no_past, page_start, page_ids, **sizes)
+        linear(out, self.w_o_padded, residual=residual, track=ctx)
 
     def attend(self, q_abs, ctx, view, page_start, page_ids):
         """[tokens, heads * kv_rank]: per head the softmax-weighted sum of the latents it sees."""

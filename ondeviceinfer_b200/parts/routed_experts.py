@@ -6,7 +6,9 @@ Steps of ``forward`` (no step waits for the host):
    choice only, the best groups, the top-k outputs and their scores as weights;
 2. ``ops.moe_group``: the (token, choice) pairs that go to real experts, sorted by expert on the device;
 3. two grouped products over that order (``csrc/grouped_gemm.cu``): gate and up with the clamped activation,
-   then down into fp32 rows;
+   then down into fp32 rows; in bfloat16, when the experts get many rows each (prompts), the rows are gathered
+   side by side instead and every expert's two products go through ``linear`` (the tensor-core kernels), for
+   which the host reads the experts' offsets once: the only wait of the part, and never inside a graph capture;
 4. ``ops.moe_combine``: each token adds its weighted rows, in the order of its choices, and its own input for
    an identity output;
 5. the shared expert, if any: gate/up product, the same activation with its own limit, down with the residual add.
@@ -23,8 +25,12 @@ from .base import Part, register_part
 from .linear import linear
 
 
+# From this many rows per expert on (on average) a bfloat16 step runs each expert's products through linear().
+ROWS_PER_EXPERT_FOR_TENSOR_CORES = 32
+
+
 class RoutedExperts(Part):
-    graph_safe = True   # no host work that depends on the step's values
+    graph_safe = True   # the grouped products wait for no one; the per-expert form is not chosen while capturing
 
     def __init__(self, spec: RoutedExpertsSpec) -> None:
         super().__init__(spec)
@@ -81,14 +87,30 @@ class RoutedExperts(Part):
         if s.num_experts > 0:
             ops.moe_group(ids, self.counts, table)
             act = torch.empty((table.n_pairs, s.expert_size), dtype=x.dtype, device=dev)
-            ops.grouped_gemm_routed(x, self.w_gate_up, act, table, gather=True, epi=ops.GROUPED_GATED_CLAMP,
-                                    limit=s.limit, alpha=s.gate_alpha)
-            ops.grouped_gemm_routed(act, self.w_down, expert_out, table, gather=False, epi=ops.GROUPED_STORE_F32)
+            if (x.dtype == torch.bfloat16 and table.n_pairs >= ROWS_PER_EXPERT_FOR_TENSOR_CORES * s.num_experts
+                    and not torch.cuda.is_current_stream_capturing()):
+                self._experts_one_by_one(x, table, act, expert_out)
+            else:
+                ops.grouped_gemm_routed(x, self.w_gate_up, act, table, gather=True, epi=ops.GROUPED_GATED_CLAMP,
+                                        limit=s.limit, alpha=s.gate_alpha)
+                ops.grouped_gemm_routed(act, self.w_down, expert_out, table, gather=False, epi=ops.GROUPED_STORE_F32)
         ops.moe_combine(residual, expert_out, x, ids, weights, table)
         if s.shared_size > 0:
             act = torch.empty((n, s.shared_size), dtype=x.dtype, device=dev)
             ops.gated_clamp(linear(x, self.w_shared_gate_up), act, s.shared_limit, s.gate_alpha)
             linear(act, self.w_shared_down, residual=residual, track=ctx)
+
+
+    def _experts_one_by_one(self, x, table, act, expert_out) -> None:
+        s = self.spec
+        rows = torch.empty((table.n_pairs, s.hidden_size), dtype=x.dtype, device=x.device)
+        ops.moe_gather(x, table, rows)
+        bounds = table.offsets.tolist()                     # waits for the device
+        for e in range(s.num_experts):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi > lo:
+                ops.gated_clamp(linear(rows[lo:hi], self.w_gate_up[e]), act[lo:hi], s.limit, s.gate_alpha)
+                expert_out[lo:hi].copy_(linear(act[lo:hi], self.w_down[e], out_dtype=torch.float32))
 
 
 register_part(RoutedExpertsSpec, RoutedExperts)
