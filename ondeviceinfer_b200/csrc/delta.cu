@@ -13,7 +13,8 @@
 //  conv_state  the state after the step: the last K-1 inputs of the sequence;
 //  prep        per (token, head): unit q (scaled), unit k, decay g as fp32 [tokens, heads, 3, d], and beta;
 //  rule        the recurrence: a block per (sequence, head, block of 32 value columns); a column of S is
-//              spread over RS neighbouring lanes, each holding d / RS of its rows in registers; the token's
+//              spread over RS neighbouring lanes (about 8 rows each, so that a token's two dot products are
+//              short chains and a shuffle tree), each holding d / RS of its rows in registers; the token's
 //              q, k, g, v and beta are staged through shared memory 8 tokens at a time;
 //  out_norm    per (token, head): o / rms(o) (eps inside the root) * weight * sigmoid(gate), rounded to T.
 #include "common.cuh"
@@ -22,7 +23,7 @@
 #error "compile with -DODI_DELTA_DIM=<key size of a head>"
 #endif
 #define D ODI_DELTA_DIM
-#define RS (D <= 32 ? 1 : (D <= 64 ? 2 : (D <= 128 ? 4 : 8)))   // lanes that share a column of S
+#define RS (D <= 8 ? 1 : (D <= 16 ? 2 : (D <= 32 ? 4 : (D <= 64 ? 8 : 16))))   // lanes that share a column of S
 #define RPT ((D + RS - 1) / RS)                                 // rows of S per lane
 #define CB 32                                                   // value columns per block
 #define TCH 8                                                   // tokens staged at a time
@@ -148,7 +149,6 @@ delta_rule_kernel(DeltaArgs a) {
     const int i = rs + RS * ii;
     S[ii] = (live && i < D) ? S_g[(size_t)i * a.dv + c] : 0.f;
   }
-  const int v_off = 2 * a.kv_heads * D + h * a.dv;   // the head's value channels in the convolution output
 
   for (int t0 = 0; t0 < q_len; t0 += TCH) {
     const int nt = min(TCH, q_len - t0);

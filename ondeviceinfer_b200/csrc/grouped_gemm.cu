@@ -13,7 +13,8 @@
 // g = min(gate, limit), u = clamp(up, -limit, limit), C = g * sigmoid(alpha * g) * (u + 1) as T).
 //
 // Tile: TM rows x 64 features per block of 256 threads, K in slices of 16 or 32 through shared memory (fp32).
-// TM = 64 (4 x 4 outputs a thread) or 16 (1 x 4), chosen by the caller from the rows a group has.
+// TM = 64 (4 x 4 outputs a thread) or 16 (1 x 4), chosen by the caller from the rows a group has; for groups
+// of a few rows there is a form that streams the weights through registers only (grouped_gemv_kernel).
 #include "common.cuh"
 
 #define TN 64
@@ -83,33 +84,42 @@ grouped_gemm_kernel(GroupedArgs a) {
   const int tx = tid & 15, ty = tid >> 4;
   float acc[GATED ? 2 : 1][RPT][4] = {};
 
+  // VEC: the pieces of the next slice are requested while the current one is multiplied
+  float va[8], vw[GATED ? 2 : 1][8];
+  const int piece = tid & 3, vrow = tid >> 2;
+  auto fetch = [&](int k0) {
+    const int k = k0 + piece * 8;
+    const int src = tid < TM * 4 ? arow[vrow] : -1;
+    if (src >= 0 && k < a.K) load8<T>(A + (size_t)src * a.lda + k, va);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) va[i] = 0.f;
+    }
+    const bool in = n0 + vrow < a.N && k < a.K;
+#pragma unroll
+    for (int s = 0; s < (GATED ? 2 : 1); ++s) {
+      if (in) load8<T>(W + (size_t)(s * a.N + n0 + vrow) * a.ldw + k, vw[s]);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vw[s][i] = 0.f;
+      }
+    }
+  };
+  if (VEC) fetch(0);
+
   for (int k0 = 0; k0 < a.K; k0 += TK) {
     __syncthreads();
     if (VEC) {
-      const int piece = tid & 3, k = k0 + piece * 8;     // four pieces of 8 k per row
-      float v[8];
       if (tid < TM * 4) {
-        const int r = tid >> 2, src = arow[r];
-        if (src >= 0 && k < a.K) load8<T>(A + (size_t)src * a.lda + k, v);
-        else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) v[i] = 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) As[SIDX(piece * 8 + i, r, ASTR)] = v[i];
+        for (int i = 0; i < 8; ++i) As[SIDX(piece * 8 + i, vrow, ASTR)] = va[i];
       }
-      const int n = tid >> 2;
-      const bool in = n0 + n < a.N && k < a.K;
 #pragma unroll
       for (int s = 0; s < (GATED ? 2 : 1); ++s) {
-        if (in) load8<T>(W + (size_t)(s * a.N + n0 + n) * a.ldw + k, v);
-        else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) v[i] = 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) Ws[s][SIDX(piece * 8 + i, n, WSTR)] = v[i];
+        for (int i = 0; i < 8; ++i) Ws[s][SIDX(piece * 8 + i, vrow, WSTR)] = vw[s][i];
       }
+      if (k0 + TK < a.K) fetch(k0 + TK);
     } else {
       for (int i = tid; i < TM * TK; i += 256) {
         const int r = i / TK, k = i % TK;
@@ -162,12 +172,154 @@ grouped_gemm_kernel(GroupedArgs a) {
   }
 }
 
+// Few rows per group (single-token steps): no tile of the weights in shared memory.  A block takes up to 4 rows
+// of one group and 64 features (32 in the gated form); the rows wait in shared memory as floats, each of the 8 warps takes 8 weight
+// rows (for the gated form 4 features: their gate and up rows), a lane reads 8 consecutive k of each weight row
+// per step (16-byte loads, eight in flight) and keeps one sum per weight row and input row; sums are reduced over
+// the lanes at the end (a fixed tree: the result of a row does not depend on the other rows of the launch).
+// Needs what VEC needs.
+#define GV_ROWS 4
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256, 2)
+grouped_gemv_kernel(GroupedArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float xs[];       // [GV_ROWS][K]
+  __shared__ int arow[GV_ROWS];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int group, row0, rows;
+  if (a.tile_group != nullptr) {
+    const int t = blockIdx.x;
+    if (t >= a.n_tiles[0]) return;
+    group = a.tile_group[t]; row0 = a.tile_row0[t]; rows = a.tile_rows[t];
+  } else {
+    group = blockIdx.z; row0 = blockIdx.x * GV_ROWS; rows = min(GV_ROWS, a.M - row0);
+  }
+  if (tid < GV_ROWS) {
+    int r = -1;
+    if (tid < rows) r = a.row_index != nullptr ? a.row_index[row0 + tid] / a.index_div : row0 + tid;
+    arow[tid] = r;
+  }
+  __syncthreads();
+  const T* A = (const T*)a.A + (a.tile_group != nullptr ? 0 : (size_t)group * a.a_group_off);
+  const T* W = (const T*)a.W + (size_t)group * a.w_group_stride;
+  for (int i = tid * 8; i < GV_ROWS * a.K; i += 256 * 8) {
+    const int r = i / a.K, k = i % a.K;
+    float v[8];
+    if (arow[r] >= 0) load8<T>(A + (size_t)arow[r] * a.lda + k, v);
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) xs[i + j] = v[j];
+  }
+  __syncthreads();
+  // weight row j of this warp: plain form feature n0 + warp * 8 + j; gated form feature n0 + warp * 4 + j / 2,
+  // its gate row (j even) or up row (j odd)
+  const int n0 = blockIdx.y * (GATED ? 32 : 64);      // 8 warps x 8 weight rows: 64 features, or 32 gated ones
+  const T* wrow[8];
+  bool wlive[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int n = GATED ? n0 + warp * 4 + (j >> 1) : n0 + warp * 8 + j;
+    wlive[j] = n < a.N;
+    wrow[j] = W + (size_t)((GATED && (j & 1)) ? a.N + n : n) * a.ldw;
+  }
+  float acc[8][GV_ROWS] = {};
+  for (int k = lane * 8; k < a.K; k += 256) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {       // four weight rows at a time: fewer registers, two blocks per SM
+      float w[4][8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (wlive[half * 4 + j]) load8<T>(wrow[half * 4 + j] + k, w[j]);
+        else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) w[j][e] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < GV_ROWS; ++r) {
+        const float4 x0 = *(const float4*)&xs[r * a.K + k], x1 = *(const float4*)&xs[r * a.K + k + 4];
+        const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[half * 4 + j][r] = fmaf(w[j][e], x[e], acc[half * 4 + j][r]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int r = 0; r < GV_ROWS; ++r) acc[j][r] = warp_sum(acc[j][r]);
+  if (lane != 0) return;
+#pragma unroll
+  for (int r = 0; r < GV_ROWS; ++r) {
+    if (r >= rows) continue;
+    const size_t crow = (size_t)(row0 + r) * a.ldc + (a.tile_group != nullptr ? 0 : (size_t)group * a.c_group_off);
+    if (GATED) {
+#pragma unroll
+      for (int f = 0; f < 4; ++f) {
+        const int n = n0 + warp * 4 + f;
+        if (n >= a.N) continue;
+        const float g = fminf(acc[2 * f][r], a.limit);
+        const float u = fminf(fmaxf(acc[2 * f + 1][r], -a.limit), a.limit);
+        ((T*)a.C)[crow + n] = from_f<T>(g / (1.f + expf(-a.alpha * g)) * (u + 1.f));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int n = n0 + warp * 8 + j;
+        if (n >= a.N) continue;
+        if (a.epi == 1) ((float*)a.C)[crow + n] = acc[j][r];
+        else ((T*)a.C)[crow + n] = from_f<T>(acc[j][r]);
+      }
+    }
+  }
+}
+
 // max_tiles: with a tile table, the most tiles the table can hold (the grid's width); tm: 16 or 64 (the
-// table must have been built for the same tm).
+// table must have been built for the same tm); tm = 4 asks for the form for few rows, which needs aligned
+// operands (odi_grouped_gemm_takes_few_rows says whether it can run).
+static bool vector_loads(const GroupedArgs& a) {
+  return a.K % 8 == 0 && a.lda % 8 == 0 && a.ldw % 8 == 0 && a.a_group_off % 8 == 0 && a.w_group_stride % 8 == 0 &&
+         (uintptr_t)a.A % 16 == 0 && (uintptr_t)a.W % 16 == 0;
+}
+
+extern "C" int odi_grouped_gemm_takes_few_rows(const GroupedArgs* args) {
+  return vector_loads(*args) && (size_t)GV_ROWS * args->K * sizeof(float) <= 200 * 1024;
+}
+
 extern "C" int odi_grouped_gemm(const GroupedArgs* args, int max_tiles, int tm, int dtype, cudaStream_t stream) {
   const GroupedArgs a = *args;
   if (a.N <= 0 || a.groups <= 0) return 0;
-  if (a.K <= 0 || (tm != 16 && tm != 64) || a.epi < 0 || a.epi > 2) return ODI_ERR_ARGUMENT;
+  if (a.K <= 0 || (tm != GV_ROWS && tm != 16 && tm != 64) || a.epi < 0 || a.epi > 2) return ODI_ERR_ARGUMENT;
+  if (tm == GV_ROWS) {
+    if (!odi_grouped_gemm_takes_few_rows(args)) return ODI_ERR_UNSUPPORTED;
+    dim3 grid;
+    const int per_block = a.epi == 2 ? 32 : 64;
+    if (a.tile_group != nullptr) {
+      if (max_tiles <= 0) return 0;
+      grid = dim3(max_tiles, (a.N + per_block - 1) / per_block, 1);
+    } else {
+      if (a.M <= 0) return 0;
+      grid = dim3((a.M + GV_ROWS - 1) / GV_ROWS, (a.N + per_block - 1) / per_block, a.groups);
+      if (grid.z > 65535) return ODI_ERR_UNSUPPORTED;
+    }
+    if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)GV_ROWS * a.K * sizeof(float);
+#define ODI_GV(T, G) \
+    do { cudaError_t e = cudaFuncSetAttribute(grouped_gemv_kernel<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+         if (e != cudaSuccess) return (int)e; \
+         odi_rc = launch_pdl((grouped_gemv_kernel<T, G>), grid, dim3(256), smem, stream, a); } while (0)
+    const bool g = a.epi == 2;
+    if (dtype == 0) { if (g) ODI_GV(float, true); else ODI_GV(float, false); }
+    else { if (g) ODI_GV(bf16, true); else ODI_GV(bf16, false); }
+#undef ODI_GV
+    return launch_status();
+  }
   dim3 grid;
   if (a.tile_group != nullptr) {
     if (max_tiles <= 0) return 0;
@@ -178,10 +330,7 @@ extern "C" int odi_grouped_gemm(const GroupedArgs* args, int max_tiles, int tm, 
     if (grid.z > 65535) return ODI_ERR_UNSUPPORTED;
   }
   if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
-  const size_t elem = dtype == 0 ? 4 : 2;
-  const bool vec = a.K % 8 == 0 && a.lda % 8 == 0 && a.ldw % 8 == 0 && a.a_group_off % 8 == 0 &&
-                   a.w_group_stride % 8 == 0 && (uintptr_t)a.A % 16 == 0 && (uintptr_t)a.W % 16 == 0 &&
-                   ((size_t)a.N * a.ldw * elem) % 16 == 0;
+  const bool vec = vector_loads(a);
 #define ODI_GG(T, TM, G) \
   do { if (vec) odi_rc = launch_pdl((grouped_gemm_kernel<T, TM, G, true>), grid, dim3(256), 0, stream, a); \
        else odi_rc = launch_pdl((grouped_gemm_kernel<T, TM, G, false>), grid, dim3(256), 0, stream, a); } while (0)

@@ -959,9 +959,21 @@ class _GroupedArgs(Structure):
 GROUPED_STORE, GROUPED_STORE_F32, GROUPED_GATED_CLAMP = 0, 1, 2
 
 
-def grouped_rows_tile(rows_per_group: float) -> int:
-    """Row tile of the grouped product for groups of about this many rows: 16 or 64."""
+FEW_ROWS = 4      # row tile of the grouped product's form for single-token steps (weights through registers only)
+
+
+def grouped_rows_tile(rows_per_group: float, few_rows_ok: bool = False) -> int:
+    """Row tile of the grouped product for groups of about this many rows: 4 (if the operands allow the form for
+    few rows), 16 or 64."""
+    if few_rows_ok and rows_per_group <= FEW_ROWS:
+        return FEW_ROWS
     return 64 if rows_per_group > 32 else 16
+
+
+def grouped_few_rows_ok(K_values: Sequence[int], dtype: torch.dtype) -> bool:
+    """Whether products over these inner sizes can take the form for few rows (multiples of 8, and four rows of
+    floats within the shared memory of a block)."""
+    return all(K % 8 == 0 and 4 * FEW_ROWS * K <= 200 * 1024 for K in K_values)
 
 
 def grouped_gemm_heads(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, a_col: int, a_stride: int, c_col: int,
@@ -980,8 +992,8 @@ def grouped_gemm_heads(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, a_c
                         None, None, None, None, None, a_stride, N * K, c_stride, a.shape[1], K, c.shape[1], M, N, K,
                         groups, 1, GROUPED_STORE_F32 if out_f32 else GROUPED_STORE, 0.0, 0.0)
     lib = load_library("grouped_gemm")
-    _check(lib.odi_grouped_gemm(byref(args), c_int(0), c_int(grouped_rows_tile(M)), c_int(dtype_code(w.dtype)),
-                                _stream()), "grouped_gemm")
+    tm = grouped_rows_tile(M, M <= 2 * FEW_ROWS and bool(lib.odi_grouped_gemm_takes_few_rows(byref(args))))
+    _check(lib.odi_grouped_gemm(byref(args), c_int(0), c_int(tm), c_int(dtype_code(w.dtype)), _stream()), "grouped_gemm")
 
 
 def grouped_gemm_routed(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, table: "RoutingTable", *, gather: bool,
@@ -1038,9 +1050,9 @@ class RoutingTable:
     """The (token, choice) pairs of a step sorted by expert, made on the device by :func:`moe_group`: ``perm`` the
     sorted order, ``pos`` each pair's place in it, and the table of row tiles the grouped products walk."""
 
-    def __init__(self, n_tokens: int, top: int, n_experts: int, device) -> None:
+    def __init__(self, n_tokens: int, top: int, n_experts: int, device, few_rows_ok: bool = False) -> None:
         self.n_pairs, self.top, self.n_experts = n_tokens * top, top, n_experts
-        self.tm = grouped_rows_tile(self.n_pairs / max(n_experts, 1))
+        self.tm = grouped_rows_tile(self.n_pairs / max(n_experts, 1), few_rows_ok)
         self.max_tiles = -(-self.n_pairs // self.tm) + n_experts
         ints = torch.empty(3 * self.n_pairs + n_experts + 1 + 3 * self.max_tiles + 1, dtype=torch.int32, device=device)
         cuts = [self.n_pairs, self.n_pairs, self.n_pairs, n_experts + 1, self.max_tiles, self.max_tiles, self.max_tiles, 1]

@@ -7,8 +7,9 @@ Steps of ``forward`` (no step waits for the host):
 2. ``ops.moe_group``: the (token, choice) pairs that go to real experts, sorted by expert on the device;
 3. two grouped products over that order (``csrc/grouped_gemm.cu``): gate and up with the clamped activation,
    then down into fp32 rows; in bfloat16, when the experts get many rows each (prompts), the rows are gathered
-   side by side instead and every expert's two products go through ``linear`` (the tensor-core kernels), for
-   which the host reads the experts' offsets once: the only wait of the part, and never inside a graph capture;
+   side by side instead and the two products go to the tensor cores: the vendor library's grouped product
+   over the experts' row ranges where it has one, else every expert's products through ``linear``, for which the
+   host reads the experts' offsets once (the only wait of the part, and never inside a graph capture);
 4. ``ops.moe_combine``: each token adds its weighted rows, in the order of its choices, and its own input for
    an identity output;
 5. the shared expert, if any: gate/up product, the same activation with its own limit, down with the residual add.
@@ -31,6 +32,7 @@ ROWS_PER_EXPERT_FOR_TENSOR_CORES = 32
 
 class RoutedExperts(Part):
     graph_safe = True   # the grouped products wait for no one; the per-expert form is not chosen while capturing
+    _library_groups = True      # until the vendor library's grouped product has refused once
 
     def __init__(self, spec: RoutedExpertsSpec) -> None:
         super().__init__(spec)
@@ -82,7 +84,9 @@ class RoutedExperts(Part):
         ids = torch.empty((n, s.top_k), dtype=torch.int32, device=dev)
         weights = torch.empty((n, s.top_k), dtype=torch.float32, device=dev)
         ops.moe_route(logits, self.correction, ids, weights, n_groups=s.num_groups, keep=s.keep_groups)
-        table = ops.RoutingTable(n, s.top_k, max(s.num_experts, 1), dev)
+        # single-token steps, a few rows per expert: the grouped product that streams weights through registers
+        few_ok = ops.grouped_few_rows_ok((s.hidden_size, s.expert_size), x.dtype)
+        table = ops.RoutingTable(n, s.top_k, max(s.num_experts, 1), dev, few_rows_ok=few_ok)
         expert_out = torch.empty((table.n_pairs, s.hidden_size), dtype=torch.float32, device=dev)
         if s.num_experts > 0:
             ops.moe_group(ids, self.counts, table)
@@ -105,6 +109,20 @@ class RoutedExperts(Part):
         s = self.spec
         rows = torch.empty((table.n_pairs, s.hidden_size), dtype=x.dtype, device=x.device)
         ops.moe_gather(x, table, rows)
+        if self._library_groups and s.hidden_size % 8 == 0 and s.expert_size % 8 == 0:
+            # the vendor library's grouped product: the experts' row ranges stay on the device, nothing waits
+            try:
+                ends = table.offsets[1:]
+                gate_up = torch._grouped_mm(rows, self.w_gate_up.transpose(1, 2), offs=ends)
+                ops.gated_clamp(gate_up, act, s.limit, s.gate_alpha)
+                expert_out.copy_(torch._grouped_mm(act, self.w_down.transpose(1, 2), offs=ends))
+                ops.LAUNCHES["library"] += 2
+                return
+            except (RuntimeError, AttributeError, TypeError, NotImplementedError) as error:
+                RoutedExperts._library_groups = False           # this build of the library has none: one by one
+                import sys
+                print(f"[ondeviceinfer_b200] no grouped product in the vendor library ({type(error).__name__}); "
+                      "routed experts run one by one", file=sys.stderr)
         bounds = table.offsets.tolist()                     # waits for the device
         for e in range(s.num_experts):
             lo, hi = bounds[e], bounds[e + 1]

@@ -47,7 +47,8 @@ def close(actual, reference, dtype, what, routed):
     gone to another expert, and the test weights are large so that every mechanism shows: median at most 4e-2,
     four rows in five at most 1e-1 (comparisons of fewer than ten rows are made together with others)."""
     if dtype == "float32":
-        assert_logits_close(actual, reference, dtype, what)
+        # the recurrent state sums over every earlier token of the sequence: sums of about a thousand terms
+        assert_logits_close(actual, reference, dtype, what, longest_sum=1024)
         return
     actual, reference = actual.float().cpu(), reference.float().cpu()
     assert actual.shape == reference.shape and torch.isfinite(actual).all(), what
@@ -106,15 +107,18 @@ def test_router_chooses_like_the_plain_router(experts, identity, top, groups, ke
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("tokens", [1, 5, 700])
-def test_routed_products_against_a_loop_over_pairs(dtype, tokens):
+@pytest.mark.parametrize("K,F", [(44, 36), (96, 40)])         # element by element; eight elements at a time
+def test_routed_products_against_a_loop_over_pairs(dtype, tokens, K, F):
     g = torch.Generator().manual_seed(tokens)
-    E, ident, top, K, F = 5, 2, 3, 44, 36
+    E, ident, top = 5, 2, 3
     x = torch.randn(tokens, K, generator=g).to(dtype)
     w_gu = (torch.randn(E, 2 * F, K, generator=g) / K ** 0.5).to(dtype)
     w_d = (torch.randn(E, K, F, generator=g) / F ** 0.5).to(dtype)
     ids = torch.stack([torch.randperm(E + ident, generator=g)[:top] for _ in range(tokens)]).int()
     weights = torch.rand(tokens, top, generator=g)
-    table = ops.RoutingTable(tokens, top, E, "cuda")
+    # aligned sizes and few rows per expert: the form that streams the weights through registers
+    table = ops.RoutingTable(tokens, top, E, "cuda", few_rows_ok=ops.grouped_few_rows_ok((K, F), dtype))
+    assert table.tm == (4 if K % 8 == 0 and tokens <= 5 else 16 if tokens <= 5 else 64)
     counts = torch.zeros(E, dtype=torch.int32, device="cuda")
     ops.moe_group(ids.cuda(), counts, table)
     assert int(counts.abs().sum()) == 0                    # left clean for the next step
@@ -136,18 +140,20 @@ def test_routed_products_against_a_loop_over_pairs(dtype, tokens):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_products_per_head(dtype):
+@pytest.mark.parametrize("heads,K,N,M,a_gap,c_gap", [(3, 10, 7, 37, 2, 4), (4, 16, 12, 3, 8, 4), (4, 16, 12, 7, 8, 4),
+                                                     (2, 24, 70, 130, 8, 2)])
+def test_products_per_head(dtype, heads, K, N, M, a_gap, c_gap):
     g = torch.Generator().manual_seed(3)
-    heads, K, N, M = 3, 10, 7, 37
-    a = torch.randn(M, heads * (K + 2) + 5, generator=g).to(dtype)     # a head's K lanes lie 12 apart, after 0
+    a = torch.randn(M, heads * (K + a_gap) + 8, generator=g).to(dtype)     # a head's K lanes lie K + a_gap apart
     w = torch.randn(heads, N, K, generator=g).to(dtype)
-    c = torch.zeros((M, heads * (N + 4)), dtype=dtype, device="cuda")
-    ops.grouped_gemm_heads(a.cuda(), w.cuda(), c, a_col=0, a_stride=K + 2, c_col=0, c_stride=N + 4, K=K)
+    c = torch.zeros((M, heads * (N + c_gap)), dtype=dtype, device="cuda")
+    ops.grouped_gemm_heads(a.cuda(), w.cuda(), c, a_col=0, a_stride=K + a_gap, c_col=0, c_stride=N + c_gap, K=K)
     for h in range(heads):
-        want = a[:, h * (K + 2):h * (K + 2) + K].double() @ w[h].double().T
-        got = c[:, h * (N + 4):h * (N + 4) + N].cpu().double()
-        assert (got - want).abs().max() < (1e-4 if dtype == torch.float32 else 6e-2)
-        assert float(c[:, h * (N + 4) + N:(h + 1) * (N + 4)].abs().max()) == 0.0       # lanes between heads untouched
+        want = a[:, h * (K + a_gap):h * (K + a_gap) + K].double() @ w[h].double().T
+        got = c[:, h * (N + c_gap):h * (N + c_gap) + N].cpu().double()
+        bound = 1e-4 if dtype == torch.float32 else 2e-2 + 1e-2 * want.abs()      # one rounding of the result
+        assert ((got - want).abs() <= bound).all()
+        assert float(c[:, h * (N + c_gap) + N:(h + 1) * (N + c_gap)].abs().max()) == 0.0       # lanes between heads untouched
 
 
 # ----------------------------------------------------------------------------- each mixer alone, whole models
