@@ -120,9 +120,33 @@ attention_simt_kernel(AttnArgs a) {
     const size_t base = (((size_t)page * a.nkv + hk) * a.page_size + (kbase % a.page_size)) * D;
     const T* kp = (const T*)a.k_pool + base;
     const int nkeys = min(KT, pos_hi + 1 - kbase);
-    for (int i = tid; i < KT * D; i += NWARPS * 32) {
-      const int j = i / D, dd = i % D;
-      Ks[j * KSTR + dd] = j < nkeys ? to_f<T>(kp[i]) : 0.f;
+    if (D % 8 == 0 && ((uintptr_t)kp % 16) == 0) {
+      // eight lanes of a row at a time (16-byte loads of bf16, two of floats)
+      for (int i = tid * 8; i < KT * D; i += NWARPS * 32 * 8) {
+        const int j = i / D, dd = i % D;
+        float v[8];
+        if (j < nkeys) {
+          if (sizeof(T) == 2) {
+            const uint4 raw = *(const uint4*)(kp + i);
+            const __nv_bfloat162* h2 = (const __nv_bfloat162*)&raw;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+          } else {
+            const float4 lo = *(const float4*)(kp + i), hi = *(const float4*)(kp + i + 4);
+            v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = 0.f;
+        }
+        *(float4*)&Ks[j * KSTR + dd] = make_float4(v[0], v[1], v[2], v[3]);
+        *(float4*)&Ks[j * KSTR + dd + 4] = make_float4(v[4], v[5], v[6], v[7]);
+      }
+    } else {
+      for (int i = tid; i < KT * D; i += NWARPS * 32) {
+        const int j = i / D, dd = i % D;
+        Ks[j * KSTR + dd] = j < nkeys ? to_f<T>(kp[i]) : 0.f;
+      }
     }
 #if !ODI_SHARED_KV
     const T* vp = (const T*)a.v_pool +

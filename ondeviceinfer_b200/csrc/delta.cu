@@ -15,7 +15,8 @@
 //  rule        the recurrence: a block per (sequence, head, block of 32 value columns); a column of S is
 //              spread over RS neighbouring lanes (about 8 rows each, so that a token's two dot products are
 //              short chains and a shuffle tree), each holding d / RS of its rows in registers; the token's
-//              q, k, g, v and beta are staged through shared memory 8 tokens at a time;
+//              q, k, g, v and beta are staged through shared memory 16 (8 for wide heads) tokens at a time, the next
+//              chunk being requested into registers while the current one is worked through;
 //  out_norm    per (token, head): o / rms(o) (eps inside the root) * weight * sigmoid(gate), rounded to T.
 #include "common.cuh"
 
@@ -26,7 +27,10 @@
 #define RS (D <= 8 ? 1 : (D <= 16 ? 2 : (D <= 32 ? 4 : (D <= 64 ? 8 : 16))))   // lanes that share a column of S
 #define RPT ((D + RS - 1) / RS)                                 // rows of S per lane
 #define CB 32                                                   // value columns per block
-#define TCH 8                                                   // tokens staged at a time
+#define TCH (D <= 128 ? 16 : 8)                                 // tokens staged at a time
+#define NTH (CB * RS)                                           // threads of the recurrence
+#define NPRE ((TCH * 3 * D + NTH - 1) / NTH)                    // staged floats of q, k, g per thread and chunk
+#define NVPRE ((TCH * CB + NTH - 1) / NTH)                      // staged values per thread and chunk
 #define MAX_TAPS 16
 
 struct DeltaArgs {
@@ -150,19 +154,42 @@ delta_rule_kernel(DeltaArgs a) {
     S[ii] = (live && i < D) ? S_g[(size_t)i * a.dv + c] : 0.f;
   }
 
+  // the chunk that starts at token t0, requested into registers
+  float pre[NPRE], vpre[NVPRE], bpre = 0.f;
+  auto request = [&](int t0) {
+    const int nt = min(TCH, q_len - t0);
+#pragma unroll
+    for (int j = 0; j < NPRE; ++j) {
+      const int i = tid + j * NTH;
+      const int tt = i / (3 * D), e = i % (3 * D);
+      pre[j] = i < nt * 3 * D ? a.qkg[((size_t)(q_begin + t0 + tt) * a.heads + h) * 3 * D + e] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < NVPRE; ++j) {
+      const int i = tid + j * NTH;
+      const int tt = i / CB, cc = i % CB;
+      vpre[j] = (i < nt * CB && c0 + cc < a.dv) ? a.o[(size_t)(q_begin + t0 + tt) * a.heads * a.dv + h * a.dv + c0 + cc] : 0.f;
+    }
+    if (tid < nt) bpre = a.beta[(size_t)(q_begin + t0 + tid) * a.heads + h];
+  };
+  if (q_len > 0) request(0);
+
   for (int t0 = 0; t0 < q_len; t0 += TCH) {
     const int nt = min(TCH, q_len - t0);
     __syncthreads();
-    for (int i = tid; i < nt * 3 * D; i += CB * RS) {
-      const int tt = i / (3 * D), e = i % (3 * D);
-      qkg_s[tt][e] = a.qkg[((size_t)(q_begin + t0 + tt) * a.heads + h) * 3 * D + e];
+#pragma unroll
+    for (int j = 0; j < NPRE; ++j) {
+      const int i = tid + j * NTH;
+      if (i < TCH * 3 * D) (&qkg_s[0][0])[i] = pre[j];
     }
-    for (int i = tid; i < nt * CB; i += CB * RS) {
-      const int tt = i / CB, cc = i % CB;
-      v_s[tt][cc] = c0 + cc < a.dv ? a.o[(size_t)(q_begin + t0 + tt) * a.heads * a.dv + h * a.dv + c0 + cc] : 0.f;
+#pragma unroll
+    for (int j = 0; j < NVPRE; ++j) {
+      const int i = tid + j * NTH;
+      if (i < TCH * CB) (&v_s[0][0])[i] = vpre[j];
     }
-    if (tid < nt) b_s[tid] = a.beta[(size_t)(q_begin + t0 + tid) * a.heads + h];
+    if (tid < TCH) b_s[tid] = bpre;
     __syncthreads();
+    if (t0 + TCH < q_len) request(t0 + TCH);      // in flight while this chunk's tokens are worked through
     for (int tt = 0; tt < nt; ++tt) {
       const float* qv = qkg_s[tt];
       const float* kv = qv + D;

@@ -187,7 +187,7 @@ __global__ void moe_combine_kernel(CombineArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  for (int i = threadIdx.x; i < a.H; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < a.H; i += gridDim.y * blockDim.x) {
     float sum = 0.f;
     for (int k = 0; k < a.top; ++k) {
       const int p = t * a.top + k;
@@ -205,8 +205,11 @@ extern "C" int odi_moe_combine(const CombineArgs* args, int dtype, cudaStream_t 
   const CombineArgs a = *args;
   if (a.n_tokens <= 0) return 0;
   const int threads = a.H >= 1024 ? 256 : 128;
-  if (dtype == 0) odi_rc = launch_pdl((moe_combine_kernel<float>), dim3(a.n_tokens), dim3(threads), 0, stream, a);
-  else odi_rc = launch_pdl((moe_combine_kernel<bf16>), dim3(a.n_tokens), dim3(threads), 0, stream, a);
+  // few tokens: a row's lanes over several blocks, so that each thread has one short chain of loads
+  const int pieces = a.n_tokens >= 512 ? 1 : min(16, (a.H + threads - 1) / threads);
+  const dim3 grid(a.n_tokens, pieces);
+  if (dtype == 0) odi_rc = launch_pdl((moe_combine_kernel<float>), grid, dim3(threads), 0, stream, a);
+  else odi_rc = launch_pdl((moe_combine_kernel<bf16>), grid, dim3(threads), 0, stream, a);
   return launch_status();
 }
 

@@ -156,7 +156,7 @@ class LatentAttention(Part):
         if ctx.max_q_len == 1:
             # single tokens: cut long key ranges so that enough blocks run side by side
             blocks = ctx.n_seqs * ((s.num_heads + 15) // 16)
-            splits = max(1, min(32, 296 // max(blocks, 1), (ctx.max_kv_len + 255) // 256))
+            splits = max(1, min(32, 592 // max(blocks, 1), (ctx.max_kv_len + 63) // 64))
             if splits > 1:
                 partial = torch.empty((ctx.n_tokens * s.num_heads * splits * (s.kv_rank + 2),), dtype=torch.float32,
                                       device=q_abs.device)
