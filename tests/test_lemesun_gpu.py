@@ -7,6 +7,12 @@ token to another expert than the plain implementation does, which changes that r
 bfloat16 comparisons of models with routed experts hold nine rows in ten to the bfloat16 bound, and every row of
 models without (``close``)."""
 
+import copy
+import json
+import subprocess
+import sys
+from pathlib import Path
+
 import pytest
 import torch
 
@@ -287,3 +293,31 @@ def test_greedy_generation_through_the_entry_point(tmp_path_factory):
                 logits = plain.forward(cfg, weights, ids)[-1]
                 assert float(logits.max() - logits[token]) < 1e-4, "the generated token is not the plain argmax"
                 ids.append(token)
+
+
+def test_command_line_writes_a_random_model_and_generates_from_it(tmp_path):
+    """``random-model`` needs the two bottleneck widths in the configuration (no tensors give them yet); the folder it
+    writes loads like any other, and ``generate`` produces the plain implementation's greedy tokens."""
+    cfg = copy.deepcopy(plain.TINY_B)
+    for layer in cfg["layers"]:
+        if layer["type"] == "channel_delta":
+            layer["mixer"].update(decay_rank=5, gate_rank=7)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    root = Path(__file__).resolve().parent.parent
+    run = lambda *a: subprocess.run([sys.executable, "-m", "ondeviceinfer_b200", *a], cwd=root, text=True,
+                                    capture_output=True, timeout=600)
+    made = run("random-model", "--config", str(tmp_path / "config.json"), "--seed", "3", "--out", str(tmp_path / "model"))
+    assert made.returncode == 0, made.stderr
+    done = run("generate", "--model", str(tmp_path / "model"), "--prompt-ids", "5,9,2,40,7", "--dtype", "float32",
+               "--max-new-tokens", "4", "--warmup-runs", "0", "--repeats", "1", "--output", str(tmp_path / "report.json"))
+    assert done.returncode == 0, done.stderr
+    report = json.loads((tmp_path / "report.json").read_text())
+    from ondeviceinfer_b200.weights import SafetensorsSource
+    source = SafetensorsSource(tmp_path / "model")
+    weights = {n: source.fetch(n).double() for n in source.stored()}
+    ids = [5, 9, 2, 40, 7]
+    for token in report["measurements"][0]["output_token_ids"]:
+        logits = plain.forward(cfg, weights, ids)[-1]
+        assert float(logits.max() - logits[token]) < 1e-4
+        ids.append(token)
+    assert len(ids) == 9
