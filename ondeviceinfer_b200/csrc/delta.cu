@@ -25,7 +25,8 @@
 #endif
 #define D ODI_DELTA_DIM
 #define RS (D <= 8 ? 1 : (D <= 16 ? 2 : (D <= 32 ? 4 : (D <= 64 ? 8 : 16))))   // lanes that share a column of S
-#define RPT ((D + RS - 1) / RS)                                 // rows of S per lane
+#define RPT ((D + RS - 1) / RS)                                 // rows of S per lane: rows rs * RPT .. of its column
+#define ROW_OK(i) ((RPT * RS == D) || (i) < D)                   // no test where the rows divide evenly
 #define CB 32                                                   // value columns per block
 #define TCH (D <= 128 ? 16 : 8)                                 // tokens staged at a time
 #define NTH (CB * RS)                                           // threads of the recurrence
@@ -137,7 +138,7 @@ __global__ void __launch_bounds__(CB * RS)
 delta_rule_kernel(DeltaArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float qkg_s[TCH][3 * D];
+  __shared__ __align__(16) float qkg_s[TCH][3 * D];
   __shared__ float v_s[TCH][CB];
   __shared__ float b_s[TCH];
   const int seq = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * CB;
@@ -150,8 +151,8 @@ delta_rule_kernel(DeltaArgs a) {
   float S[RPT];
 #pragma unroll
   for (int ii = 0; ii < RPT; ++ii) {
-    const int i = rs + RS * ii;
-    S[ii] = (live && i < D) ? S_g[(size_t)i * a.dv + c] : 0.f;
+    const int i = rs * RPT + ii;
+    S[ii] = (live && ROW_OK(i)) ? S_g[(size_t)i * a.dv + c] : 0.f;
   }
 
   // the chunk that starts at token t0, requested into registers
@@ -197,8 +198,8 @@ delta_rule_kernel(DeltaArgs a) {
       float dot = 0.f;
 #pragma unroll
       for (int ii = 0; ii < RPT; ++ii) {
-        const int i = rs + RS * ii;
-        if (i < D) { S[ii] *= gv[i]; dot = fmaf(S[ii], kv[i], dot); }
+        const int i = rs * RPT + ii;
+        if (ROW_OK(i)) { S[ii] *= gv[i]; dot = fmaf(S[ii], kv[i], dot); }
       }
 #pragma unroll
       for (int o = RS >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
@@ -206,8 +207,8 @@ delta_rule_kernel(DeltaArgs a) {
       float out = 0.f;
 #pragma unroll
       for (int ii = 0; ii < RPT; ++ii) {
-        const int i = rs + RS * ii;
-        if (i < D) { S[ii] = fmaf(kv[i], u, S[ii]); out = fmaf(S[ii], qv[i], out); }
+        const int i = rs * RPT + ii;
+        if (ROW_OK(i)) { S[ii] = fmaf(kv[i], u, S[ii]); out = fmaf(S[ii], qv[i], out); }
       }
 #pragma unroll
       for (int o = RS >> 1; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
@@ -218,8 +219,8 @@ delta_rule_kernel(DeltaArgs a) {
   if (live) {
 #pragma unroll
     for (int ii = 0; ii < RPT; ++ii) {
-      const int i = rs + RS * ii;
-      if (i < D) S_g[(size_t)i * a.dv + c] = S[ii];
+      const int i = rs * RPT + ii;
+      if (ROW_OK(i)) S_g[(size_t)i * a.dv + c] = S[ii];
     }
   }
 }

@@ -174,12 +174,12 @@ extern "C" int odi_moe_group(const GroupingArgs* args, cudaStream_t stream) {
 
 struct CombineArgs {
   float* residual;        // [n_tokens, H], added to in place
-  const float* expert_out;  // [n_pairs, H] rows in the sorted order
+  const void* expert_out;   // [n_pairs, H] rows in the sorted order: fp32, or T if out_is_t
   const void* input;      // [n_tokens, H] in T: what identity outputs pass on
   const int* ids;
   const float* weights;
   const int* pos;
-  int n_tokens, H, top, n_experts;
+  int n_tokens, H, top, n_experts, out_is_t;
 };
 
 template <typename T>
@@ -193,8 +193,10 @@ __global__ void moe_combine_kernel(CombineArgs a) {
       const int p = t * a.top + k;
       const int e = a.ids[p];
       if (e < 0) continue;
-      const float v = e < a.n_experts ? a.expert_out[(size_t)a.pos[p] * a.H + i]
-                                      : to_f<T>(((const T*)a.input)[(size_t)t * a.H + i]);
+      float v;
+      if (e >= a.n_experts) v = to_f<T>(((const T*)a.input)[(size_t)t * a.H + i]);
+      else if (a.out_is_t) v = to_f<T>(((const T*)a.expert_out)[(size_t)a.pos[p] * a.H + i]);
+      else v = ((const float*)a.expert_out)[(size_t)a.pos[p] * a.H + i];
       sum = fmaf(a.weights[p], v, sum);
     }
     a.residual[(size_t)t * a.H + i] += sum;

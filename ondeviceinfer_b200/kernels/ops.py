@@ -1089,20 +1089,23 @@ def moe_gather(x: torch.Tensor, table: RoutingTable, out: torch.Tensor) -> None:
 class _CombineArgs(Structure):
     _fields_ = [("residual", c_void_p), ("expert_out", c_void_p), ("input", c_void_p), ("ids", c_void_p),
                 ("weights", c_void_p), ("pos", c_void_p), ("n_tokens", c_int), ("H", c_int), ("top", c_int),
-                ("n_experts", c_int)]
+                ("n_experts", c_int), ("out_is_t", c_int)]
 
 
 def moe_combine(residual: torch.Tensor, expert_out: torch.Tensor, x: torch.Tensor, ids: torch.Tensor,
                 weights: torch.Tensor, table: RoutingTable) -> None:
-    """residual[t] += sum_k weights[t, k] * (row pos[t, k] of ``expert_out``, or ``x[t]`` for an identity output)."""
+    """residual[t] += sum_k weights[t, k] * (row pos[t, k] of ``expert_out``, or ``x[t]`` for an identity output).
+    ``expert_out`` is fp32, or in the dtype of ``x``."""
     _require(residual, "residual", torch.float32, 2)
-    _require(expert_out, "expert_out", torch.float32, 2)
+    _require(expert_out, "expert_out", ndim=2)
     _require(x, "x", ndim=2)
+    if expert_out.dtype not in (torch.float32, x.dtype):
+        raise KernelError("expert_out is float32 or has the dtype of x")
     n, H = residual.shape
     if x.shape != (n, H) or expert_out.shape != (table.n_pairs, H) or ids.numel() != table.n_pairs:
         raise KernelError("moe_combine sizes disagree")
     args = _CombineArgs(_ptr(residual), _ptr(expert_out), _ptr(x), _ptr(ids), _ptr(weights), _ptr(table.pos), n, H,
-                        table.top, table.n_experts)
+                        table.top, table.n_experts, 0 if expert_out.dtype == torch.float32 else 1)
     lib = load_library("moe")
     _check(lib.odi_moe_combine(byref(args), c_int(dtype_code(x.dtype)), _stream()), "moe_combine")
 

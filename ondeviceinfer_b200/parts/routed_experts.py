@@ -93,7 +93,7 @@ class RoutedExperts(Part):
             act = torch.empty((table.n_pairs, s.expert_size), dtype=x.dtype, device=dev)
             if (x.dtype == torch.bfloat16 and table.n_pairs >= ROWS_PER_EXPERT_FOR_TENSOR_CORES * s.num_experts
                     and not torch.cuda.is_current_stream_capturing()):
-                self._experts_one_by_one(x, table, act, expert_out)
+                expert_out = self._experts_one_by_one(x, table, act, expert_out)
             else:
                 ops.grouped_gemm_routed(x, self.w_gate_up, act, table, gather=True, epi=ops.GROUPED_GATED_CLAMP,
                                         limit=s.limit, alpha=s.gate_alpha)
@@ -105,7 +105,8 @@ class RoutedExperts(Part):
             linear(act, self.w_shared_down, residual=residual, track=ctx)
 
 
-    def _experts_one_by_one(self, x, table, act, expert_out) -> None:
+    def _experts_one_by_one(self, x, table, act, expert_out):
+        """The experts' outputs in the sorted order of pairs: ``expert_out``, or a tensor of the library's own."""
         s = self.spec
         rows = torch.empty((table.n_pairs, s.hidden_size), dtype=x.dtype, device=x.device)
         ops.moe_gather(x, table, rows)
@@ -115,9 +116,9 @@ class RoutedExperts(Part):
                 ends = table.offsets[1:]
                 gate_up = torch._grouped_mm(rows, self.w_gate_up.transpose(1, 2), offs=ends)
                 ops.gated_clamp(gate_up, act, s.limit, s.gate_alpha)
-                expert_out.copy_(torch._grouped_mm(act, self.w_down.transpose(1, 2), offs=ends))
+                down = torch._grouped_mm(act, self.w_down.transpose(1, 2), offs=ends)
                 ops.LAUNCHES["library"] += 2
-                return
+                return down                                   # rounded to the compute dtype; the combine widens it
             except (RuntimeError, AttributeError, TypeError, NotImplementedError) as error:
                 RoutedExperts._library_groups = False           # this build of the library has none: one by one
                 import sys
@@ -129,6 +130,7 @@ class RoutedExperts(Part):
             if hi > lo:
                 ops.gated_clamp(linear(rows[lo:hi], self.w_gate_up[e]), act[lo:hi], s.limit, s.gate_alpha)
                 expert_out[lo:hi].copy_(linear(act[lo:hi], self.w_down[e], out_dtype=torch.float32))
+        return expert_out
 
 
 register_part(RoutedExpertsSpec, RoutedExperts)
