@@ -13,8 +13,8 @@
 //  conv_state  the state after the step: the last K-1 inputs of the sequence;
 //  prep        per (token, head): unit q (scaled), unit k, decay g as fp32 [tokens, heads, 3, d], and beta;
 //  rule        the recurrence: a block per (sequence, head, block of 32 value columns); a column of S is
-//              spread over RS neighbouring lanes (about 8 rows each, so that a token's two dot products are
-//              short chains and a shuffle tree), each holding d / RS of its rows in registers; the token's
+//              spread over RS neighbouring lanes (8, or a whole warp for wide heads, so that a token's two dot
+//              products are a few FMAs and a shuffle tree), each holding d / RS of its rows in registers; the token's
 //              q, k, g, v and beta are staged through shared memory 16 (8 for wide heads) tokens at a time, the next
 //              chunk being requested into registers while the current one is worked through;
 //  out_norm    per (token, head): o / rms(o) (eps inside the root) * weight * sigmoid(gate), rounded to T.
@@ -24,8 +24,15 @@
 #error "compile with -DODI_DELTA_DIM=<key size of a head>"
 #endif
 #define D ODI_DELTA_DIM
-#define RS (D <= 8 ? 1 : (D <= 16 ? 2 : (D <= 32 ? 4 : (D <= 64 ? 8 : 16))))   // lanes that share a column of S
-#define RPT ((D + RS - 1) / RS)                                 // rows of S per lane: rows rs * RPT .. of its column
+#ifdef ODI_DELTA_RS
+#define RS ODI_DELTA_RS                                          // a sweep's choice (a power of two up to 32)
+#else
+// lanes that share a column of S.  Measured on B200 inside whole prompts of 2,048 tokens (us for the mixer):
+// key size 64, 16 heads: 8 lanes 881, 32 lanes 1,084; key size 128, 32 heads: 16 lanes 2,200, 32 lanes 1,742.
+#define RS (D <= 8 ? 1 : (D <= 16 ? 2 : (D <= 32 ? 4 : (D <= 64 ? 8 : 32))))
+#endif
+#define RPT ((D + RS - 1) / RS)                                 // rows of S per lane: every RS-th row of its column (neighbouring lanes read
+                                                                // neighbouring words of shared memory; rows side by side per lane measured slower)
 #define ROW_OK(i) ((RPT * RS == D) || (i) < D)                   // no test where the rows divide evenly
 #define CB 32                                                   // value columns per block
 #define TCH (D <= 128 ? 16 : 8)                                 // tokens staged at a time
@@ -151,7 +158,7 @@ delta_rule_kernel(DeltaArgs a) {
   float S[RPT];
 #pragma unroll
   for (int ii = 0; ii < RPT; ++ii) {
-    const int i = rs * RPT + ii;
+    const int i = rs + RS * ii;
     S[ii] = (live && ROW_OK(i)) ? S_g[(size_t)i * a.dv + c] : 0.f;
   }
 
@@ -198,7 +205,7 @@ delta_rule_kernel(DeltaArgs a) {
       float dot = 0.f;
 #pragma unroll
       for (int ii = 0; ii < RPT; ++ii) {
-        const int i = rs * RPT + ii;
+        const int i = rs + RS * ii;
         if (ROW_OK(i)) { S[ii] *= gv[i]; dot = fmaf(S[ii], kv[i], dot); }
       }
 #pragma unroll
@@ -207,7 +214,7 @@ delta_rule_kernel(DeltaArgs a) {
       float out = 0.f;
 #pragma unroll
       for (int ii = 0; ii < RPT; ++ii) {
-        const int i = rs * RPT + ii;
+        const int i = rs + RS * ii;
         if (ROW_OK(i)) { S[ii] = fmaf(kv[i], u, S[ii]); out = fmaf(S[ii], qv[i], out); }
       }
 #pragma unroll
@@ -219,7 +226,7 @@ delta_rule_kernel(DeltaArgs a) {
   if (live) {
 #pragma unroll
     for (int ii = 0; ii < RPT; ++ii) {
-      const int i = rs * RPT + ii;
+      const int i = rs + RS * ii;
       if (ROW_OK(i)) S_g[(size_t)i * a.dv + c] = S[ii];
     }
   }
