@@ -3,6 +3,8 @@
 //
 // One block per token reads its row of the projection output
 //   [ head 0: d plain lanes, r rotated lanes | head 1 ... | R latent lanes | r shared rotated key lanes ]
+// (cache rows and absorbed queries may be wider than R + r, `row` lanes, so that R + r need not be a multiple of
+// four; the lanes beyond are zero on both sides and add nothing to a score)
 // and
 //  * norms the R latent lanes (RMS over R in fp32, times a plain weight, eps inside the root), rounds them
 //    once to T and writes them to lanes 0..R-1 of the token's row in the paged cache;
@@ -30,6 +32,7 @@ struct LatentPrepArgs {
   float eps;
   void* latent_out;      // null, or [n_tokens, R] in T: the normed latent once more, rows side by side
   void* key_rot_out;     // null, or [n_tokens, r] in T: the rotated shared key lanes once more
+  int row;               // lanes of a cache row and of a head's absorbed query: R + r, or more (lanes beyond stay zero)
 };
 
 __device__ __forceinline__ void rotated_pair(int lane, int rot_dims, int interleaved, int* a, int* b, int* i) {
@@ -60,7 +63,7 @@ latent_prep_kernel(LatentPrepArgs a) {
   const T* down = row + q_width;
   const float* cs = a.cos_t + (size_t)t * (a.rot_dims / 2);
   const float* sn = a.sin_t + (size_t)t * (a.rot_dims / 2);
-  const int W = a.R + a.r;
+  const int W = a.row;
 
   float ss = 0.f;
   for (int i = threadIdx.x; i < a.R; i += blockDim.x) { const float v = to_f<T>(down[i]); ss += v * v; }
@@ -93,7 +96,7 @@ latent_prep_kernel(LatentPrepArgs a) {
 // pools [pages, heads, page_size, Dh] of the step's own, where sequence s holds pages page_start[s].. in order.
 struct LatentExpandArgs {
   const void* proj;      // [n_tokens, ld]: per head d plain query lanes (then r lanes that are not read here)
-  const void* q_abs;     // [n_tokens, heads, R + r]: the rotated query lanes at R..
+  const void* q_abs;     // [n_tokens, heads, row]: the rotated query lanes at R..
   const void* k_plain;   // [n_tokens, heads * d]
   const void* key_rot;   // [n_tokens, r]
   const void* v;         // [n_tokens, heads * dv]
@@ -103,7 +106,7 @@ struct LatentExpandArgs {
   const int* tok_seq;
   const int* cu_q;
   const int* page_start;
-  int n_tokens, ld, heads, d, r, R, dv, Dh, page_size;
+  int n_tokens, ld, heads, d, r, R, dv, Dh, page_size, row;
 };
 
 template <typename T>
@@ -116,7 +119,7 @@ latent_expand_kernel(LatentExpandArgs a) {
   const int li = t - a.cu_q[seq];
   const size_t slot = ((size_t)(a.page_start[seq] + li / a.page_size) * a.heads + h) * a.page_size + li % a.page_size;
   const T* qp = (const T*)a.proj + (size_t)t * a.ld + h * (a.d + a.r);
-  const T* qr = (const T*)a.q_abs + ((size_t)t * a.heads + h) * (a.R + a.r) + a.R;
+  const T* qr = (const T*)a.q_abs + ((size_t)t * a.heads + h) * a.row + a.R;
   const T* kp = (const T*)a.k_plain + ((size_t)t * a.heads + h) * a.d;
   const T* kr = (const T*)a.key_rot + (size_t)t * a.r;
   const T* vp = (const T*)a.v + ((size_t)t * a.heads + h) * a.dv;
@@ -144,7 +147,7 @@ extern "C" int odi_latent_expand(const LatentExpandArgs* args, int dtype, cudaSt
 extern "C" int odi_latent_prep(const LatentPrepArgs* args, int dtype, cudaStream_t stream) {
   const LatentPrepArgs a = *args;
   if (a.n_tokens <= 0) return 0;
-  if (a.rot_dims % 2 != 0 || a.rot_dims > a.r || a.R <= 0 || a.heads <= 0) return ODI_ERR_ARGUMENT;
+  if (a.rot_dims % 2 != 0 || a.rot_dims > a.r || a.R <= 0 || a.heads <= 0 || a.row < a.R + a.r) return ODI_ERR_ARGUMENT;
   if (dtype == 0) odi_rc = launch_pdl((latent_prep_kernel<float>), dim3(a.n_tokens), dim3(128), 0, stream, a);
   else odi_rc = launch_pdl((latent_prep_kernel<bf16>), dim3(a.n_tokens), dim3(128), 0, stream, a);
   return launch_status();

@@ -881,22 +881,27 @@ class _LatentPrepArgs(Structure):
                 ("page_start", c_void_p), ("page_ids", c_void_p),
                 ("n_tokens", c_int), ("ld", c_int), ("heads", c_int), ("d", c_int), ("r", c_int), ("R", c_int),
                 ("rot_dims", c_int), ("interleaved", c_int), ("page_size", c_int), ("ring_pages", c_int),
-                ("write_cache", c_int), ("eps", c_float), ("latent_out", c_void_p), ("key_rot_out", c_void_p)]
+                ("write_cache", c_int), ("eps", c_float), ("latent_out", c_void_p), ("key_rot_out", c_void_p),
+                ("row", c_int)]
 
 
 def latent_prep(proj: torch.Tensor, q_abs: torch.Tensor, pool: torch.Tensor, norm_w: torch.Tensor, cos_t, sin_t,
                 tok_seq, tok_pos, page_start, page_ids, *, heads: int, d: int, r: int, R: int, rot_dims: int,
                 interleaved: bool, page_size: int, ring_pages: int, write_cache: bool, eps: float,
-                latent_out: Optional[torch.Tensor] = None, key_rot_out: Optional[torch.Tensor] = None) -> None:
+                latent_out: Optional[torch.Tensor] = None, key_rot_out: Optional[torch.Tensor] = None,
+                row: Optional[int] = None) -> None:
     """From the fused query / down projection ``proj`` [tokens, heads (d + r) + R + r]: the normed latent and the
     rotated shared key lanes into the token's cache row, each head's rotated query lanes into lanes R.. of
-    ``q_abs`` [tokens, heads, R + r] (see ``csrc/latent.cu``)."""
+    ``q_abs`` [tokens, heads, row] (see ``csrc/latent.cu``).  ``row`` (default R + r) is the width of a cache row and
+    of a head's absorbed query; lanes beyond R + r are left as they are (zero)."""
+    row = R + r if row is None else row
     _require(proj, "proj", ndim=2)
     _require(q_abs, "q_abs", proj.dtype)
     _require(pool, "pool", proj.dtype)
     _require(norm_w, "norm_w", torch.float32, 1)
     n = proj.shape[0]
-    if proj.shape[1] != heads * (d + r) + R + r or q_abs.numel() != n * heads * (R + r) or norm_w.numel() != R:
+    if (proj.shape[1] != heads * (d + r) + R + r or q_abs.numel() != n * heads * row or norm_w.numel() != R
+            or row < R + r or pool.shape[-1] != row):
         raise KernelError("latent_prep sizes disagree")
     if rot_dims > 0:
         _require(cos_t, "cos_t", torch.float32, 2)
@@ -913,7 +918,7 @@ def latent_prep(proj: torch.Tensor, q_abs: torch.Tensor, pool: torch.Tensor, nor
     args = _LatentPrepArgs(_ptr(proj), _ptr(q_abs), _ptr(pool), _ptr(norm_w), _ptr(cos_t), _ptr(sin_t), _ptr(tok_seq),
                            _ptr(tok_pos), _ptr(page_start), _ptr(page_ids), n, proj.shape[1], heads, d, r, R, rot_dims,
                            1 if interleaved else 0, page_size, ring_pages, 1 if write_cache else 0, eps,
-                           _ptr(latent_out), _ptr(key_rot_out))
+                           _ptr(latent_out), _ptr(key_rot_out), row)
     lib = load_library("latent")
     _check(lib.odi_latent_prep(byref(args), c_int(dtype_code(proj.dtype)), _stream()), "latent_prep")
 
@@ -923,11 +928,11 @@ class _LatentExpandArgs(Structure):
                 ("q_full", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p), ("tok_seq", c_void_p),
                 ("cu_q", c_void_p), ("page_start", c_void_p),
                 ("n_tokens", c_int), ("ld", c_int), ("heads", c_int), ("d", c_int), ("r", c_int), ("R", c_int),
-                ("dv", c_int), ("Dh", c_int), ("page_size", c_int)]
+                ("dv", c_int), ("Dh", c_int), ("page_size", c_int), ("row", c_int)]
 
 
 def latent_expand(proj, q_abs, k_plain, key_rot, v, q_full, k_pool, v_pool, tok_seq, cu_q, page_start, *, heads: int,
-                  d: int, r: int, R: int, dv: int, Dh: int, page_size: int) -> None:
+                  d: int, r: int, R: int, dv: int, Dh: int, page_size: int, row: Optional[int] = None) -> None:
     """Whole heads of ``Dh`` lanes for prompts that start their sequences (``csrc/latent.cu``): queries into ``q_full``
     [tokens, heads, Dh], keys and values into pools [pages, heads, page_size, Dh] where sequence s holds the pages
     from ``page_start[s]`` on, in order."""
@@ -940,7 +945,7 @@ def latent_expand(proj, q_abs, k_plain, key_rot, v, q_full, k_pool, v_pool, tok_
         raise KernelError("latent_expand sizes disagree")
     args = _LatentExpandArgs(_ptr(proj), _ptr(q_abs), _ptr(k_plain), _ptr(key_rot), _ptr(v), _ptr(q_full), _ptr(k_pool),
                              _ptr(v_pool), _ptr(tok_seq), _ptr(cu_q), _ptr(page_start), n, proj.shape[1], heads, d, r, R,
-                             dv, Dh, page_size)
+                             dv, Dh, page_size, R + r if row is None else row)
     lib = load_library("latent")
     _check(lib.odi_latent_expand(byref(args), c_int(dtype_code(proj.dtype)), _stream()), "latent_expand")
 

@@ -46,13 +46,15 @@ class LatentAttention(Part):
         for key in ("num_heads", "qk_dim", "v_dim", "kv_rank"):
             if getattr(spec, key) <= 0:
                 raise ValueError(f"{key} must be positive, got {getattr(spec, key)}")
-        if spec.rot_dim < 0 or (spec.kv_rank + spec.rot_dim) % 4 != 0:
-            raise ValueError(f"kv_rank + rot_dim must be a multiple of 4 (got {spec.kv_rank} + {spec.rot_dim}): "
-                             "the attention kernel reads cache rows four lanes at a time")
+        if spec.rot_dim < 0:
+            raise ValueError("rot_dim must not be negative")
         self.position = build_part(spec.position)
         if self.position.rot_dim > spec.rot_dim:
             raise ValueError("the position encoding rotates more lanes than the heads have rotated lanes")
-        self.row = spec.kv_rank + spec.rot_dim        # width of a cache row and of an absorbed query
+        # width of a cache row and of an absorbed query: the attention kernel reads rows four lanes at a time, so
+        # the lanes are rounded up and the ones beyond kv_rank + rot_dim stay zero in the cache and in the query
+        self.row = -(-(spec.kv_rank + spec.rot_dim) // 4) * 4
+        self.padded = self.row != spec.kv_rank + spec.rot_dim
         # lanes of a whole head (query/key: plain + rotated; value), in the steps of 16 the prefill kernels take
         self.head_lanes = -(-max(spec.qk_dim + spec.rot_dim, spec.v_dim) // 16) * 16
 
@@ -95,7 +97,8 @@ class LatentAttention(Part):
         proj = linear(x, self.w_in)
         tables = self.position.rotary_tables(ctx)
         cos, sin = tables if tables is not None else (None, None)
-        q_abs = torch.empty((n, s.num_heads * self.row), dtype=proj.dtype, device=proj.device)
+        q_abs = (torch.zeros if self.padded else torch.empty)((n, s.num_heads * self.row), dtype=proj.dtype,
+                                                              device=proj.device)
         whole_heads = (self.w_o_padded is not None and ctx.max_q_len >= WHOLE_HEADS_MIN_TOKENS
                        and not any(ctx.past_lens) and not torch.cuda.is_current_stream_capturing())
         latent = torch.empty((n, s.kv_rank), dtype=proj.dtype, device=proj.device) if whole_heads else None
@@ -105,7 +108,7 @@ class LatentAttention(Part):
                         rot_dims=self.position.rot_dim if cos is not None else 0,
                         interleaved=getattr(self.position, "interleaved", False), page_size=PAGE_SIZE,
                         ring_pages=group.ring_pages, write_cache=view.writes_kv, eps=s.norm_eps,
-                        latent_out=latent, key_rot_out=key_rot)
+                        latent_out=latent, key_rot_out=key_rot, row=self.row)
         if whole_heads:
             self._attend_whole_heads(proj, q_abs, latent, key_rot, ctx, residual)
             return
@@ -138,7 +141,7 @@ class LatentAttention(Part):
         q_full = torch.empty((n, s.num_heads * lanes), dtype=proj.dtype, device=dev)
         ops.latent_expand(proj, q_abs, k_plain, key_rot, values, q_full, pools[0], pools[1], ctx.tok_seq, ctx.cu_q,
                           page_start, heads=s.num_heads, d=s.qk_dim, r=s.rot_dim, R=s.kv_rank, dv=s.v_dim, Dh=lanes,
-                          page_size=PAGE_SIZE)
+                          page_size=PAGE_SIZE, row=self.row)
         out = torch.empty_like(q_full)
         sizes = dict(n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_heads, d=lanes,
                      page_size=PAGE_SIZE, scale=s.scale)

@@ -202,6 +202,9 @@ TINY_B = model_config(61, 64, 1e-6, [
 # one mixer alone, no feed-forward
 ONLY_LATENT = model_config(53, 32, 1e-6, [latent_layer(4, 8, 8, 8, 16, 0.35, 1000.0, None)])
 ONLY_DELTA = model_config(53, 32, 1e-6, [delta_layer(4, 2, 16, 12, 4, None)])
+# heads of 48 + 16 = 64 lanes (the size of the tcgen05 prefill kernel), and a latent row of 21 + 6 lanes (no multiple of 4)
+LATENT_64 = model_config(53, 64, 1e-6, [latent_layer(2, 48, 16, 32, 40, 0.125, 10000.0, None),
+                                        latent_layer(3, 10, 6, 8, 21, 0.25, 300.0, None)])
 BOTTLENECKS = (6, 10)     # widths of the decay and gate bottlenecks in every test model
 
 

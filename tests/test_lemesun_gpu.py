@@ -24,7 +24,7 @@ from ondeviceinfer_b200.kernels import ops
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
 CONFIGS = {"A": (plain.TINY_A, 21), "B": (plain.TINY_B, 22), "latent": (plain.ONLY_LATENT, 23),
-           "delta": (plain.ONLY_DELTA, 24), "sharp": (plain.ONLY_LATENT, 25)}
+           "delta": (plain.ONLY_DELTA, 24), "sharp": (plain.ONLY_LATENT, 25), "lanes64": (plain.LATENT_64, 26)}
 _MODELS, _PLAIN = {}, {}
 
 
@@ -166,7 +166,7 @@ def test_products_per_head(dtype, heads, K, N, M, a_gap, c_gap):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["latent", "delta", "A", "B"])
+@pytest.mark.parametrize("case", ["latent", "delta", "A", "B", "lanes64"])
 def test_whole_prompts_and_first_tokens(case, dtype, tmp_path_factory):
     model = engine(case, dtype, tmp_path_factory)
     cache = model.make_cache(max_tokens=512, max_seqs=2)
@@ -183,7 +183,7 @@ def test_whole_prompts_and_first_tokens(case, dtype, tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["latent", "delta", "A", "B"])
+@pytest.mark.parametrize("case", ["latent", "delta", "A", "B", "lanes64"])
 def test_prefill_then_long_decoding_over_page_borders(case, dtype, tmp_path_factory):
     model = engine(case, dtype, tmp_path_factory)
     tokens = plain.random_prompts(CONFIGS[case][0], [200], 6)[0]
