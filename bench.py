@@ -34,6 +34,10 @@ lengths and with temperature sampling.  One JSON line is printed:
 on the same configuration, and prints the same line with ``"impl": "reference"``.  Nothing of
 this library is imported in that arm.
 
+``--design lemesun`` leaves the default workload alone and measures the second architecture instead: prefill and
+decode throughput at layer sizes like a real model's beside the dense model of equal width, one JSON line
+(``run_design_points``).
+
 Untimed steps before the timed ones: max(W, 32), in both arms and for every decode figure.  The first decode
 steps after a prefill run at the SM clock that the prefill left (the power cap pulls it down and it comes
 back within about a tenth of a second: measured here 4.29 ms a step for the first 26 steps, then 3.56), so a
