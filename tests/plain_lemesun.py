@@ -275,3 +275,37 @@ def random_prompts(cfg, lengths, seed):
 
 def widened(weights, dtype=torch.float64):
     return {k: v.to(dtype) for k, v in weights.items()}
+
+
+def random_config(seed):
+    """A valid configuration with sizes drawn from odd values (widths off the multiples of 8, one head, heads that
+    share q/k, one tap, rows that are no multiple of 4, identity outputs or none, one group or several)."""
+    g = torch.Generator().manual_seed(1000 + seed)
+
+    def pick(values):
+        return values[int(torch.randint(0, len(values), (1,), generator=g))]
+
+    def some_moe():
+        groups, per = pick([1, 2, 3]), pick([2, 3, 4])
+        n_all = groups * per
+        identity = pick([0, 1, 2]) if n_all > 2 else 0
+        keep = pick(list(range(1, groups + 1)))
+        top = pick(list(range(1, min(keep * per, 4) + 1)))
+        shared = {"ff": pick([8, 20, 36]), "limit": pick([0.5, 1.5, 4.0])} if pick([0, 1]) else None
+        return moe(n_all - identity, identity, top, groups, keep, pick([12, 20, 36]), pick([0.6, 1.5, 3.0]), shared)
+
+    width = pick([40, 52, 72, 100])
+    layers = []
+    for i in range(pick([2, 3, 4])):
+        mlp = some_moe() if pick([0, 1, 1]) else None
+        if pick([0, 1]):
+            rot = pick([2, 4, 6, 8])
+            layers.append(latent_layer(pick([1, 2, 3, 5]), pick([4, 12, 16, 20]), rot, pick([4, 12, 20]),
+                                       pick([9, 16, 22, 40]), pick([0.1, 0.3, 0.5]), pick([50.0, 10000.0, 1e6]), mlp))
+        else:
+            kv = pick([1, 2, 3])
+            layers.append(delta_layer(kv * pick([1, 2]), kv, pick([6, 12, 33, 48]), pick([5, 16, 40]), pick([1, 2, 3, 5]), mlp))
+    # one more run of an earlier layer's tensors, with a cache or state of its own
+    source = pick(list(range(len(layers))))
+    layers.append({**layers[source], "weights_of": source})
+    return model_config(pick([31, 64, 101]), width, pick([1e-6, 1e-5]), layers)
