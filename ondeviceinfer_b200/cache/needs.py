@@ -12,12 +12,14 @@ import torch
 class KVNeed:
     """Keys and values of every cached position (``window`` None) or of the last
     ``window`` positions only.  ``value_plane`` False: one row per position and head instead of a key row
-    and a value row (a compressed cache whose rows serve as both)."""
+    and a value row (a compressed cache whose rows serve as both).  ``value_dim`` not None: value rows of that
+    many lanes instead of ``head_dim``, in a pool of their own."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_plane: bool = True
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)

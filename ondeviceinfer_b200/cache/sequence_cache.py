@@ -17,7 +17,8 @@ fixed-size per-sequence state.
   keeps a ring of pages per sequence instead of all of them.
 * The layout of a key/value pool is ``[owner, 2, page, kv_head, row, head_dim]``
   (owner = a layer execution that writes its own cache; 2 = keys, values), so one
-  (page, head) tile is a dense ``[PAGE_SIZE, head_dim]`` box.
+  (page, head) tile is a dense ``[PAGE_SIZE, head_dim]`` box.  Values whose width differs
+  from the keys' (``KVNeed.value_dim``) have a pool ``[owner, page, kv_head, row, value_dim]``.
 
 Errors follow ondeviceinfer/cache.py:65-75 in spirit: capacity exceeded, unknown slot.
 """
@@ -52,8 +53,13 @@ class KVGroup:
             self.ring_pages = pages_for(need.window + max_step_tokens - 1) + 1
         # one page and one slot beyond the capacity belong to padding rows of fixed-width steps
         self.planes = 2 if need.value_plane else 1
-        self.pool = torch.zeros((len(owners), self.planes, n_pages + 1, need.num_kv_heads, PAGE_SIZE, need.head_dim),
-                                dtype=dtype, device=device)
+        # values of a width of their own live in a second pool of the same page numbering
+        self.value_pool = None
+        if need.value_plane and need.value_dim is not None and need.value_dim != need.head_dim:
+            self.value_pool = torch.zeros((len(owners), n_pages + 1, need.num_kv_heads, PAGE_SIZE, need.value_dim),
+                                          dtype=dtype, device=device)
+        self.pool = torch.zeros((len(owners), 1 if self.value_pool is not None else self.planes, n_pages + 1,
+                                 need.num_kv_heads, PAGE_SIZE, need.head_dim), dtype=dtype, device=device)
         self.pages = IndexAllocator(n_pages, "page")
         self.pad_page = n_pages
         self.slot_pages: List[List[int]] = [[] for _ in range(n_slots)] + [[self.pad_page]]
@@ -66,6 +72,8 @@ class KVGroup:
         return self.pool[owner_pos, 0]
 
     def values(self, owner_pos: int) -> Optional[torch.Tensor]:
+        if self.value_pool is not None:
+            return self.value_pool[owner_pos]
         return self.pool[owner_pos, 1] if self.planes == 2 else None
 
 
@@ -217,6 +225,7 @@ class SequenceCache:
     @property
     def storage_bytes(self) -> int:
         total = sum(g.pool.numel() * g.pool.element_size() for g in self.kv_groups)
+        total += sum(g.value_pool.numel() * g.value_pool.element_size() for g in self.kv_groups if g.value_pool is not None)
         return total + sum(g.data.numel() * g.data.element_size() for g in self.state_groups)
 
     @property

@@ -39,12 +39,15 @@ class RMSNormSpec:
 class RotarySpec:
     """Rotary position encoding over the first ``rotary_dim`` lanes of a head: lane i turns with lane
     i + rotary_dim / 2 (half-split), or, with ``interleaved``, lane 2i with lane 2i + 1; the angle of pair i at
-    position p is p * theta^(-2i / rotary_dim)."""
+    position p is p * f_i, f_i = theta^(-2i / rotary_dim).  ``scaling`` = (factor, low, high, original) slows the
+    long wavelengths: with l = 2 pi / f_i, f_i stays where l < original / high, becomes f_i / factor where
+    l > original / low, and in between is (1 - s) f_i / factor + s f_i with s = (original / l - low) / (high - low)."""
 
     head_dim: int
     theta: float
     rotary_dim: Optional[int] = None  # None: the whole head
     interleaved: bool = False
+    scaling: Optional[Tuple[float, float, float, float]] = None
 
     @property
     def dim(self) -> int:
@@ -83,6 +86,34 @@ class AttentionSpec:
 
     def has(self, role: str) -> bool:
         return role in dict(self.names)
+
+
+@dataclass(frozen=True)
+class CappedAttentionSpec:
+    """Grouped-query causal attention whose queries and keys are rotated first and then scaled to unit root mean
+    square, with a value width of its own, squashed scores and an optional window.
+
+    q and k heads have ``head_dim`` lanes, v heads ``value_dim``.  ``position`` rotates q and k; afterwards, with
+    ``unit_norm_eps`` not None, every q and k head is divided by sqrt(mean of its squares + eps) (no weight).
+    score = q . k * ``scale``; with ``softcap`` c not None, score <- c tanh(score / c); ordinary softmax over the
+    visible keys: all of 0..p, or with ``window`` w the last w of them (p itself included).  All of this in fp32.
+    ``names`` maps the roles q, k, v, o to tensor names below ``prefix``."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    position: object
+    prefix: str
+    names: Tuple[Tuple[str, str], ...]
+    softcap: Optional[float] = None
+    window: Optional[int] = None
+    unit_norm_eps: Optional[float] = None
+
+    def name(self, role: str) -> str:
+        return self.prefix + dict(self.names)[role]
 
 
 @dataclass(frozen=True)
@@ -170,6 +201,39 @@ class RoutedExpertsSpec:
 
 
 @dataclass(frozen=True)
+class TableExpertsSpec:
+    """Mixture of experts without a router: row ``token id`` of an integer table ([``vocab_size``, ``top_k``],
+    distinct entries) names the experts of a token, each weighted 1 / top_k.  An expert is down(act(up x)) without
+    biases, ``activation`` "gelu_erf" or "gelu_tanh".  ``shared_size`` > 0 adds one expert of that form for every
+    token, multiplied (``shared_gated``) by sigmoid(sg . x), one number per token.
+    Tensor names below ``prefix``: ``table``, ``e<i>.up|down``, ``shared.up|down|sg``."""
+
+    hidden_size: int
+    expert_size: int
+    num_experts: int
+    top_k: int
+    vocab_size: int
+    prefix: str
+    activation: str = "gelu_erf"
+    shared_size: int = 0
+    shared_gated: bool = True
+
+
+@dataclass(frozen=True)
+class MLPSpec:
+    """Dense feed-forward without a gate: down(act(up(x))), no biases; ``activation`` "gelu_erf" or "gelu_tanh"."""
+
+    hidden_size: int
+    intermediate_size: int
+    activation: str
+    prefix: str
+    names: Tuple[Tuple[str, str], ...]
+
+    def name(self, role: str) -> str:
+        return self.prefix + dict(self.names)[role]
+
+
+@dataclass(frozen=True)
 class GatedMLPSpec:
     """Dense gated feed-forward: down(act(gate(x)) * up(x)), no biases."""
 
@@ -191,6 +255,32 @@ class PreNormBlockSpec:
     mixer: object
     ffn_norm: object    # None together with ffn: the layer has no feed-forward
     ffn: object
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    """h += mixer_post_norm(mixer(mixer_norm(h))); h += ffn_post_norm(feed_forward(ffn_norm(h))): a norm on both
+    sides of every sublayer.  The post norms work on the fp32 output of the sublayer and add in fp32."""
+
+    mixer_norm: object
+    mixer: object
+    mixer_post_norm: object
+    ffn_norm: object    # the three of the feed-forward are None together: the layer has none
+    ffn: object
+    ffn_post_norm: object
+
+
+@dataclass(frozen=True)
+class ReinjectSpec:
+    """A step between layers that keeps no cache: h <- W [h ; e] + steps[index], with e the output of the
+    embedding, W [hidden, 2 hidden] (the columns of h first) and ``steps`` [``num_steps``, hidden].  It opens a
+    pass of a looped stack; the passes share W and differ in ``index``."""
+
+    hidden_size: int
+    weight_name: str
+    steps_name: str
+    num_steps: int
+    index: int
 
 
 @dataclass(frozen=True)
@@ -220,12 +310,13 @@ class EmbeddingSpec:
 class HeadSpec:
     """Output head: logits = rows W^T on the rows the final norm gives it.  ``weight_name`` None ties it to the
     embedding table (the model then fills in that tensor's name and sets ``tied``); with ``tied`` the head
-    binds ``weight_name`` without declaring it, because another part already does."""
+    binds ``weight_name`` without declaring it, because another part already does.  ``softcap`` squashes the logits."""
 
     vocab_size: int
     hidden_size: int
     weight_name: Optional[str]
     tied: bool = False
+    softcap: Optional[float] = None     # c: logits <- c tanh(logits / c)
 
 
 @dataclass(frozen=True)

@@ -11,6 +11,7 @@
 // memory (converted to fp32); each warp owns 4 rows; lane j scores key j of the tile;
 // the softmax is the running-maximum form in fp32; the output accumulates in fp32.
 // Key j is visible to the query at position p iff j <= p and (window == 0 or j > p - window).
+// With softcap c > 0 a score s (already times scale) becomes c tanh(s / c) before the softmax.
 //
 // With splits > 1 every split writes an un-normalised partial (acc[d], max, sum) and
 // attention_combine merges them in split order.
@@ -53,7 +54,7 @@ struct AttnArgs {
   const int* page_start;
   const int* page_ids;
   int n_seqs, nq, nkv, page_size, ring_pages, window, splits, bq, head_chunks;
-  float scale;
+  float scale, softcap;
 };
 
 template <typename T>
@@ -176,7 +177,9 @@ attention_simt_kernel(AttnArgs a) {
 #pragma unroll
     for (int r = 0; r < RW; ++r) {
       const bool vis = rpos[r] >= 0 && kj <= rpos[r] && (a.window == 0 || kj > rpos[r] - a.window);
-      const float sc = vis ? s[r] * a.scale : -INFINITY;
+      float sc = s[r] * a.scale;
+      if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
+      if (!vis) sc = -INFINITY;
       const float mx = warp_max(sc);
       const float m_new = fmaxf(m[r], mx);
       float p = 0.f, alpha = 1.f;

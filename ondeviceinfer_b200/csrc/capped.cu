@@ -1,0 +1,224 @@
+// Kernels around an attention whose queries and keys are rotated and then scaled to unit root mean square, and
+// around blocks that norm a sublayer's output before adding it:
+//
+//  * rot_unit_prep: per (token, head) the rotation of neighbouring-lane pairs over the first rot_dim lanes, the
+//    division by sqrt(mean of squares + eps), and the write of q to the query buffer, k and v to their cache pages
+//    (v has a width of its own);
+//  * activation: out = act(x), act the exact (erf) GELU or its tanh form, fp32 arithmetic, one rounding;
+//  * softcap: x <- c tanh(x / c) in place on fp32 rows (logits);
+//  * concat_cast: out[t] = [a[t] ; b[t]] of two fp32 streams in the compute dtype;
+//  * rmsnorm_add: h[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w, all fp32 (the norm after a sublayer and the
+//    residual add in one pass);
+//  * gated_row_add: acc[t] += sigmoid(x[t] . g) * y[t] (an expert that every token takes, scaled by a number per token).
+#include "common.cuh"
+
+struct RotUnitArgs {
+  const void* qkv;      // [n_tokens, nq * d + nkv * d + nkv * dv]
+  void* q_out;          // [n_tokens, nq * d]
+  void* k_pool;         // [pages, nkv, page_size, d]
+  void* v_pool;         // [pages, nkv, page_size, dv]
+  const float* cos_t;   // null: no rotation; [n_tokens, rot_dim / 2]
+  const float* sin_t;
+  const int* tok_seq;
+  const int* tok_pos;
+  const int* page_start;
+  const int* page_ids;
+  int n_tokens, nq, nkv, d, dv, rot_dim, page_size, ring_pages, write_kv, unit;
+  float eps;
+};
+
+// One warp per (token, head).  Lane i % 32 holds element i in register i / 32, so the partner of lane 2i
+// (lane 2i + 1) is the neighbouring lane of the same register.
+template <typename T, int MAXP>
+__global__ void rot_unit_prep_kernel(RotUnitArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int heads = a.nq + (a.write_kv ? 2 * a.nkv : 0);
+  const long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long)a.n_tokens * heads) return;
+  const int t = (int)(item / heads), h = (int)(item % heads);
+  const int d = a.d;
+  const size_t row = (size_t)(a.nq + a.nkv) * d + (size_t)a.nkv * a.dv;
+  const int kind = h < a.nq ? 0 : (h < a.nq + a.nkv ? 1 : 2);  // 0 q, 1 k, 2 v
+  const int pos = a.tok_pos[t];
+  const T* src;
+  T* dst;
+  if (kind == 0) {
+    src = (const T*)a.qkv + (size_t)t * row + (size_t)h * d;
+    dst = (T*)a.q_out + ((size_t)t * a.nq + h) * d;
+  } else {
+    const int hk = kind == 1 ? h - a.nq : h - a.nq - a.nkv;
+    const int s = a.tok_seq[t];
+    const int page = a.page_ids[a.page_start[s] + page_slot_of(pos, a.page_size, a.ring_pages)];
+    const size_t at = ((size_t)page * a.nkv + hk) * a.page_size + (pos % a.page_size);
+    if (kind == 1) {
+      src = (const T*)a.qkv + (size_t)t * row + (size_t)(a.nq + hk) * d;
+      dst = (T*)a.k_pool + at * d;
+    } else {
+      src = (const T*)a.qkv + (size_t)t * row + (size_t)(a.nq + a.nkv) * d + (size_t)hk * a.dv;
+      dst = (T*)a.v_pool + at * a.dv;
+      for (int i = lane; i < a.dv; i += 32) dst[i] = src[i];
+      return;
+    }
+  }
+  float x[MAXP];
+#pragma unroll
+  for (int r = 0; r < MAXP; ++r) {
+    const int i = lane + 32 * r;
+    x[r] = i < d ? to_f<T>(src[i]) : 0.f;
+  }
+  if (a.cos_t != nullptr) {
+    const int half = a.rot_dim >> 1;
+#pragma unroll
+    for (int r = 0; r < MAXP; ++r) {
+      const int i = lane + 32 * r;
+      const float other = __shfl_xor_sync(0xffffffffu, x[r], 1);
+      if (i < a.rot_dim) {
+        const float cs = a.cos_t[(size_t)t * half + (i >> 1)], sn = a.sin_t[(size_t)t * half + (i >> 1)];
+        // even lane u: u cos - v sin; odd lane v: v cos + u sin
+        x[r] = (i & 1) ? fmaf(other, sn, x[r] * cs) : fmaf(-other, sn, x[r] * cs);
+      }
+    }
+  }
+  if (a.unit) {
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < MAXP; ++r) ss += x[r] * x[r];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)d + a.eps);
+#pragma unroll
+    for (int r = 0; r < MAXP; ++r) x[r] *= inv;
+  }
+#pragma unroll
+  for (int r = 0; r < MAXP; ++r) {
+    const int i = lane + 32 * r;
+    if (i < d) dst[i] = from_f<T>(x[r]);
+  }
+}
+
+extern "C" int odi_rot_unit_prep(const RotUnitArgs* args, int dtype, cudaStream_t stream) {
+  RotUnitArgs a = *args;
+  if (a.n_tokens <= 0) return 0;
+  if (a.d > 512 || a.d <= 0 || a.dv <= 0 || (a.rot_dim & 1) || a.rot_dim > a.d) return ODI_ERR_UNSUPPORTED;
+  const int heads = a.nq + (a.write_kv ? 2 * a.nkv : 0);
+  const long items = (long)a.n_tokens * heads;
+  const int blocks = (int)((items + 3) / 4);
+#define ODI_LAUNCH(T, P) odi_rc = launch_pdl((rot_unit_prep_kernel<T, P>), dim3(blocks), dim3(128), 0, stream, a)
+  if (dtype == 0) {
+    if (a.d <= 128) ODI_LAUNCH(float, 4); else if (a.d <= 256) ODI_LAUNCH(float, 8); else ODI_LAUNCH(float, 16);
+  } else {
+    if (a.d <= 128) ODI_LAUNCH(bf16, 4); else if (a.d <= 256) ODI_LAUNCH(bf16, 8); else ODI_LAUNCH(bf16, 16);
+  }
+#undef ODI_LAUNCH
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
+
+__device__ __forceinline__ float gelu_erf(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f)); }
+__device__ __forceinline__ float gelu_tanh(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, long n, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float z = to_f<T>(x[i]);
+  out[i] = from_f<T>(kind == 0 ? gelu_erf(z) : gelu_tanh(z));
+}
+
+// kind: 0 the exact (erf) GELU, 1 its tanh form
+extern "C" int odi_activation(const void* x, void* out, long n, int kind, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (kind < 0 || kind > 1) return ODI_ERR_ARGUMENT;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == 0) odi_rc = launch_pdl((activation_kernel<float>), dim3(blocks), dim3(256), 0, stream, (const float*)x, (float*)out, n, kind);
+  else odi_rc = launch_pdl((activation_kernel<bf16>), dim3(blocks), dim3(256), 0, stream, (const bf16*)x, (bf16*)out, n, kind);
+  return launch_status();
+}
+
+__global__ void softcap_kernel(float* __restrict__ x, long n, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+extern "C" int odi_softcap(float* x, long n, float cap, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (!(cap > 0.f)) return ODI_ERR_ARGUMENT;
+  odi_rc = launch_pdl((softcap_kernel), dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, n, cap);
+  return launch_status();
+}
+
+template <typename T>
+__global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out,
+                                   long n, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long t = i / (2 * H);
+  const int c = (int)(i % (2 * H));
+  out[i] = from_f<T>(c < H ? a[t * H + c] : b[t * H + c - H]);
+}
+
+extern "C" int odi_concat_cast(const float* a, const float* b, void* out, long rows, int H, int dtype, cudaStream_t stream) {
+  const long n = rows * 2 * H;
+  if (n <= 0) return 0;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == 0) odi_rc = launch_pdl((concat_cast_kernel<float>), dim3(blocks), dim3(256), 0, stream, a, b, (float*)out, n, H);
+  else odi_rc = launch_pdl((concat_cast_kernel<bf16>), dim3(blocks), dim3(256), 0, stream, a, b, (bf16*)out, n, H);
+  return launch_status();
+}
+
+// hidden[t] += y[t] * rsqrt(mean(y[t]^2) + eps) * w: one block per row, the row read twice (the second time from cache).
+__global__ void rmsnorm_add_kernel(float* __restrict__ hidden, const float* __restrict__ y, const float* __restrict__ w,
+                                   int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const size_t base = (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = y[base + i]; ss += v * v; }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) hidden[base + i] += y[base + i] * inv * w[i];
+}
+
+extern "C" int odi_rmsnorm_add(float* hidden, const float* y, const float* w, int n, int H, float eps, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  odi_rc = launch_pdl((rmsnorm_add_kernel), dim3(n), dim3(threads), 0, stream, hidden, y, w, H, eps);
+  return launch_status();
+}
+
+// acc[t] += sigmoid(x[t] . g) * y[t]; the dot product in fp32 over the row of x (T), y fp32 or T.
+template <typename T, typename Y>
+__global__ void gated_row_add_kernel(float* __restrict__ acc, const Y* __restrict__ y, const T* __restrict__ x,
+                                     const T* __restrict__ g, int H, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const size_t t = blockIdx.x;
+  float dot = 0.f;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) dot = fmaf(to_f<T>(x[t * K + i]), to_f<T>(g[i]), dot);
+  dot = block_sum(dot, scratch);
+  const float gate = 1.0f / (1.0f + expf(-dot));
+  for (int i = threadIdx.x; i < H; i += blockDim.x) acc[t * H + i] = fmaf(gate, to_f<Y>(y[t * H + i]), acc[t * H + i]);
+}
+
+// y_is_t: y has the dtype of x; else it is fp32.
+extern "C" int odi_gated_row_add(float* acc, const void* y, const void* x, const void* g, int n, int H, int K, int y_is_t,
+                                 int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  if (dtype == 0) odi_rc = launch_pdl((gated_row_add_kernel<float, float>), dim3(n), dim3(threads), 0, stream, acc, (const float*)y, (const float*)x, (const float*)g, H, K);
+  else if (y_is_t) odi_rc = launch_pdl((gated_row_add_kernel<bf16, bf16>), dim3(n), dim3(threads), 0, stream, acc, (const bf16*)y, (const bf16*)x, (const bf16*)g, H, K);
+  else odi_rc = launch_pdl((gated_row_add_kernel<bf16, float>), dim3(n), dim3(threads), 0, stream, acc, (const float*)y, (const bf16*)x, (const bf16*)g, H, K);
+  return launch_status();
+}

@@ -10,7 +10,8 @@
 //    order reads row `row_index[i] / index_div` of A (row i itself if row_index is null) and writes row i of C.
 //
 // Epilogues: 0 store as T, 1 store as fp32, 2 gated and clamped (W_g holds N gate rows then N up rows;
-// g = min(gate, limit), u = clamp(up, -limit, limit), C = g * sigmoid(alpha * g) * (u + 1) as T).
+// g = min(gate, limit), u = clamp(up, -limit, limit), C = g * sigmoid(alpha * g) * (u + 1) as T), 3 the exact
+// (erf) GELU of the sum as T, 4 its tanh form.
 //
 // Tile: TM rows x 64 features per block of 256 threads, K in slices of 16 or 32 through shared memory (fp32).
 // TM = 64 (4 x 4 outputs a thread) or 16 (1 x 4), chosen by the caller from the rows a group has; for groups
@@ -18,6 +19,12 @@
 #include "common.cuh"
 
 #define TN 64
+
+__device__ __forceinline__ float grouped_act(float z, int epi) {
+  if (epi == 3) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+  if (epi == 4) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  return z;
+}
 
 struct GroupedArgs {
   const void* A;
@@ -166,7 +173,7 @@ grouped_gemm_kernel(GroupedArgs a) {
       } else if (a.epi == 1) {
         ((float*)a.C)[crow + n] = acc[0][i][j];
       } else {
-        ((T*)a.C)[crow + n] = from_f<T>(acc[0][i][j]);
+        ((T*)a.C)[crow + n] = from_f<T>(grouped_act(acc[0][i][j], a.epi));
       }
     }
   }
@@ -274,7 +281,7 @@ grouped_gemv_kernel(GroupedArgs a) {
         const int n = n0 + warp * 8 + j;
         if (n >= a.N) continue;
         if (a.epi == 1) ((float*)a.C)[crow + n] = acc[j][r];
-        else ((T*)a.C)[crow + n] = from_f<T>(acc[j][r]);
+        else ((T*)a.C)[crow + n] = from_f<T>(grouped_act(acc[j][r], a.epi));
       }
     }
   }
@@ -295,7 +302,7 @@ extern "C" int odi_grouped_gemm_takes_few_rows(const GroupedArgs* args) {
 extern "C" int odi_grouped_gemm(const GroupedArgs* args, int max_tiles, int tm, int dtype, cudaStream_t stream) {
   const GroupedArgs a = *args;
   if (a.N <= 0 || a.groups <= 0) return 0;
-  if (a.K <= 0 || (tm != GV_ROWS && tm != 16 && tm != 64) || a.epi < 0 || a.epi > 2) return ODI_ERR_ARGUMENT;
+  if (a.K <= 0 || (tm != GV_ROWS && tm != 16 && tm != 64) || a.epi < 0 || a.epi > 4) return ODI_ERR_ARGUMENT;
   if (tm == GV_ROWS) {
     if (!odi_grouped_gemm_takes_few_rows(args)) return ODI_ERR_UNSUPPORTED;
     dim3 grid;

@@ -5,6 +5,8 @@
 //           the router outputs form `n_groups` equal groups of neighbours, a group's score is its largest c,
 //           only members of the `keep` best groups may be chosen; the `top` largest c among them are chosen
 //           (ties: the lower index); the weight of a chosen output is its s (no renormalisation).
+//  table    routing without a router: a token's choices are row `token id` of an integer table, each with the
+//           same weight (out-of-range entries take no place).
 //  count    per (token, choice) pair whose output is a real expert: its rank among the pairs of that expert.
 //  plan     one block: the experts' offsets in the sorted order of pairs and the table of row tiles.
 //  scatter  per pair: its place in the sorted order (`pos`) and the order itself (`perm`).
@@ -103,6 +105,32 @@ extern "C" int odi_moe_route(const RouteArgs* args, cudaStream_t stream) {
   const size_t smem = sizeof(float) * 4 * (2 * (size_t)a.n_all + a.n_groups);
   if (smem > 48 * 1024) return ODI_ERR_UNSUPPORTED;
   odi_rc = launch_pdl(moe_route_kernel, dim3((a.n_tokens + 3) / 4), dim3(128), smem, stream, a);
+  return launch_status();
+}
+
+// ids[t, k] = table[token[t], k] (an entry outside [0, n_experts) becomes -1), weights[t, k] = weight.
+__global__ void moe_table_route_kernel(const int* __restrict__ table, const int* __restrict__ tokens, int* __restrict__ ids,
+                                       float* __restrict__ weights, int n_pairs, int top, int vocab, int n_experts,
+                                       float weight) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= n_pairs) return;
+  const int token = tokens[p / top];
+  int e = -1;
+  if (token >= 0 && token < vocab) e = table[(size_t)token * top + p % top];
+  if (e < 0 || e >= n_experts) e = -1;
+  ids[p] = e;
+  weights[p] = weight;
+}
+
+extern "C" int odi_moe_table_route(const int* table, const int* tokens, int* ids, float* weights, int n_tokens, int top,
+                                   int vocab, int n_experts, float weight, cudaStream_t stream) {
+  const int n_pairs = n_tokens * top;
+  if (n_pairs <= 0) return 0;
+  if (top <= 0 || vocab <= 0 || n_experts <= 0) return ODI_ERR_ARGUMENT;
+  odi_rc = launch_pdl(moe_table_route_kernel, dim3((n_pairs + 127) / 128), dim3(128), 0, stream, table, tokens, ids, weights,
+                      n_pairs, top, vocab, n_experts, weight);
   return launch_status();
 }
 

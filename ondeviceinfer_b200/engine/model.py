@@ -37,6 +37,7 @@ class DecoderModel:
         self.logits_size = head.vocab_size                   # width of the logits the head returns
         self.hidden_size = plan.embedding.hidden_size
         self.runtime: Optional[Runtime] = None
+        self.keeps_embedding = any(getattr(layer, "reads_embedding", False) for layer in self.layers)
         for i, entry in enumerate(plan.order):
             if entry.cache_from is not None:
                 mine = self.layers[entry.layer].cache_needs()
@@ -108,6 +109,8 @@ class DecoderModel:
             hidden = self.embedding.forward(ctx)           # the fp32 residual stream [tokens, hidden]
         ctx.residual_sumsq = None          # nothing is known about the rows of `hidden` yet
         ctx.pending_residual_add = None
+        if self.keeps_embedding:
+            ctx.embedded = hidden.clone()  # a layer reads the embedding's output again; the stream changes in place
         for index, entry in enumerate(self.plan.order):
             layer = self.layers[entry.layer]
             # A block that finishes deferred residual adds (parts/block.py) sets the flag for its own parts and
@@ -116,7 +119,10 @@ class DecoderModel:
             if not getattr(layer, "finishes_residual_adds", False):
                 flush_residual_add(ctx)
             with nvtx_range(f"layer_{entry.layer}"):
-                layer.forward(hidden, ctx, cache.view(index))
+                replaced = layer.forward(hidden, ctx, cache.view(index))
+            if replaced is not None:           # a layer may hand back a new stream instead of changing it in place
+                flush_residual_add(ctx)
+                hidden = replaced
         flush_residual_add(ctx)                # the last block's last product
         if ctx.n_want == 0:
             return torch.empty((0, self.logits_size), dtype=torch.float32, device=self.runtime.device)

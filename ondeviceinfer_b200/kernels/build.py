@@ -163,6 +163,7 @@ ALL_SOURCES = {
     "attention_simt": [{"ODI_HEAD_DIM": d} for d in _HEAD_SIZES_MMA + (512,)]
                       + [{"ODI_HEAD_DIM": 576, "ODI_VALUE_DIM": 512, "ODI_SHARED_KV": 1}],      # a latent cache
     "latent": [{}],
+    "capped": [{}],
     "grouped_gemm": [{}],
     "moe": [{}],
     "delta": [{"ODI_DELTA_DIM": d} for d in (64, 128)],

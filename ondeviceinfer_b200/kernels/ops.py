@@ -567,7 +567,7 @@ class _AttnArgs(Structure):
                 ("partial", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),
                 ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int), ("nkv", c_int), ("page_size", c_int),
                 ("ring_pages", c_int), ("window", c_int), ("splits", c_int), ("bq", c_int),
-                ("head_chunks", c_int), ("scale", c_float)]
+                ("head_chunks", c_int), ("scale", c_float), ("softcap", c_float)]
 
 
 SIMT_HEAD_DIMS = tuple(range(16, 513, 16))
@@ -576,14 +576,15 @@ SIMT_HEAD_DIMS = tuple(range(16, 513, 16))
 def attention_simt(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
                    nq: int, nkv: int, d: int, page_size: int, ring_pages: int, window: int, scale: float,
                    splits: int = 1, partial: Optional[torch.Tensor] = None, dv: Optional[int] = None,
-                   shared_kv: bool = False) -> None:
-    """Causal GQA over the paged cache for any mixture of prompt and decode sequences.
+                   shared_kv: bool = False, softcap: float = 0.0) -> None:
+    """Causal GQA over the paged cache for any mixture of prompt and decode sequences.  ``softcap`` c > 0:
+    scores (times ``scale``) become c tanh(score / c) before the softmax.
 
     ``dv`` (default ``d``): width of the value rows and of the output.  ``shared_kv``: a cached row is key and
     value at once (the value is its first ``dv`` lanes; ``v_pool`` is None), as in attention over a latent
     cache; ``d`` may then be any multiple of 4."""
     dv = d if dv is None else dv
-    plain = dv == d and not shared_kv
+    plain = dv == d and not shared_kv and (d in SIMT_HEAD_DIMS or d % 4 != 0 or d > 1024)
     if plain and d not in SIMT_HEAD_DIMS:
         raise KernelError(f"attention takes head sizes in steps of 16 up to 512, not {d}")
     if not plain and (d % 4 != 0 or not 4 <= d <= 1024 or dv <= 0 or (shared_kv and dv > d)):
@@ -606,7 +607,7 @@ def attention_simt(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, 
             raise KernelError(f"splits={splits} needs an fp32 partial buffer of {need} elements")
     args = _AttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(partial), _ptr(cu_q), _ptr(past),
                      _ptr(page_start), _ptr(page_ids), n_seqs, nq, nkv, page_size, ring_pages, window, splits,
-                     0, 0, scale)
+                     0, 0, scale, softcap)
     defines = {"ODI_HEAD_DIM": d}
     if not plain:
         defines.update({"ODI_VALUE_DIM": dv, "ODI_SHARED_KV": 1 if shared_kv else 0})
@@ -961,7 +962,7 @@ class _GroupedArgs(Structure):
                 ("groups", c_int), ("index_div", c_int), ("epi", c_int), ("limit", c_float), ("alpha", c_float)]
 
 
-GROUPED_STORE, GROUPED_STORE_F32, GROUPED_GATED_CLAMP = 0, 1, 2
+GROUPED_STORE, GROUPED_STORE_F32, GROUPED_GATED_CLAMP, GROUPED_GELU_ERF, GROUPED_GELU_TANH = 0, 1, 2, 3, 4
 
 
 FEW_ROWS = 4      # row tile of the grouped product's form for single-token steps (weights through registers only)
@@ -1113,6 +1114,126 @@ def moe_combine(residual: torch.Tensor, expert_out: torch.Tensor, x: torch.Tenso
                         table.top, table.n_experts, 0 if expert_out.dtype == torch.float32 else 1)
     lib = load_library("moe")
     _check(lib.odi_moe_combine(byref(args), c_int(dtype_code(x.dtype)), _stream()), "moe_combine")
+
+
+def moe_table_route(table: torch.Tensor, token_ids: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, *,
+                    n_experts: int, weight: float) -> None:
+    """Routing without a router: ``ids[t]`` = row ``token_ids[t]`` of the int32 ``table`` [vocab, top] (entries
+    outside the experts become -1), ``weights`` all ``weight``."""
+    _require(table, "table", torch.int32, 2)
+    _require(token_ids, "token_ids", torch.int32, 1)
+    _require(ids, "ids", torch.int32, 2)
+    _require(weights, "weights", torch.float32, 2)
+    n, top = ids.shape
+    if token_ids.numel() != n or table.shape[1] != top or weights.shape != ids.shape:
+        raise KernelError("table routing sizes disagree")
+    lib = load_library("moe")
+    _check(lib.odi_moe_table_route(_ptr(table), _ptr(token_ids), _ptr(ids), _ptr(weights), c_int(n), c_int(top),
+                                   c_int(table.shape[0]), c_int(n_experts), c_float(weight), _stream()), "moe_table_route")
+
+
+# ------------------------------------------------------------------------------ rotated unit heads, activations, norm-and-add
+
+
+class _RotUnitArgs(Structure):
+    _fields_ = [("qkv", c_void_p), ("q_out", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p),
+                ("cos_t", c_void_p), ("sin_t", c_void_p), ("tok_seq", c_void_p), ("tok_pos", c_void_p),
+                ("page_start", c_void_p), ("page_ids", c_void_p), ("n_tokens", c_int), ("nq", c_int), ("nkv", c_int),
+                ("d", c_int), ("dv", c_int), ("rot_dim", c_int), ("page_size", c_int), ("ring_pages", c_int),
+                ("write_kv", c_int), ("unit", c_int), ("eps", c_float)]
+
+
+def rot_unit_prep(qkv, q_out, k_pool, v_pool, cos_t, sin_t, tok_seq, tok_pos, page_start, page_ids, *, nq: int,
+                  nkv: int, d: int, dv: int, rot_dim: int, page_size: int, ring_pages: int, write_kv: bool,
+                  unit_eps: Optional[float]) -> None:
+    """Head preparation of an attention that rotates first and norms afterwards: q and k heads (``d`` lanes) of
+    ``qkv`` [tokens, nq d + nkv d + nkv dv] are rotated over their first ``rot_dim`` lanes (lane 2i with 2i + 1;
+    ``cos_t`` None: not at all) and, with ``unit_eps`` not None, divided by sqrt(mean of squares + eps); q goes to
+    ``q_out``, k and the v heads (``dv`` lanes, as they are) to the token's row of their cache pages."""
+    _require(qkv, "qkv", ndim=2)
+    _require(q_out, "q_out", qkv.dtype, 2)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (nq + nkv) * d + nkv * dv or q_out.shape != (n, nq * d):
+        raise KernelError(f"rot_unit_prep sizes disagree: qkv {tuple(qkv.shape)}, q_out {tuple(q_out.shape)}, "
+                          f"nq={nq}, nkv={nkv}, d={d}, dv={dv}")
+    if write_kv:
+        _require(k_pool, "k_pool", qkv.dtype)
+        _require(v_pool, "v_pool", qkv.dtype)
+        if k_pool.shape[-1] != d or v_pool.shape[-1] != dv:
+            raise KernelError("the cache pools do not have the heads' widths")
+    if cos_t is not None:
+        _require(cos_t, "cos_t", torch.float32, 2)
+        _require(sin_t, "sin_t", torch.float32, 2)
+        if cos_t.shape != (n, rot_dim // 2) or sin_t.shape != cos_t.shape:
+            raise KernelError("rope tables must be [tokens, rot_dim / 2]")
+    args = _RotUnitArgs(_ptr(qkv), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(cos_t), _ptr(sin_t), _ptr(tok_seq),
+                        _ptr(tok_pos), _ptr(page_start), _ptr(page_ids), n, nq, nkv, d, dv, rot_dim, page_size, ring_pages,
+                        1 if write_kv else 0, 0 if unit_eps is None else 1, 0.0 if unit_eps is None else unit_eps)
+    lib = load_library("capped")
+    _check(lib.odi_rot_unit_prep(byref(args), c_int(dtype_code(qkv.dtype)), _stream()), "rot_unit_prep")
+
+
+ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out = act(x) elementwise (fp32 arithmetic, one rounding); ``kind`` "gelu_erf" or "gelu_tanh"."""
+    _require(x, "x")
+    _require(out, "out", x.dtype)
+    if kind not in ACTIVATIONS or out.numel() != x.numel():
+        raise KernelError(f"activation {kind!r} on {tuple(x.shape)} -> {tuple(out.shape)}")
+    lib = load_library("capped")
+    _check(lib.odi_activation(_ptr(x), _ptr(out), c_long(x.numel()), c_int(ACTIVATIONS[kind]), c_int(dtype_code(x.dtype)),
+                              _stream()), "activation")
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place (fp32)."""
+    _require(x, "x", torch.float32)
+    lib = load_library("capped")
+    _check(lib.odi_softcap(_ptr(x), c_long(x.numel()), c_float(cap), _stream()), "softcap")
+
+
+def concat_cast(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = [a[t] ; b[t]] for fp32 ``a`` and ``b`` [tokens, H], in the dtype of ``out`` [tokens, 2 H]."""
+    _require(a, "a", torch.float32, 2)
+    _require(b, "b", torch.float32, 2)
+    _require(out, "out", ndim=2)
+    n, H = a.shape
+    if b.shape != (n, H) or out.shape != (n, 2 * H):
+        raise KernelError("concat_cast sizes disagree")
+    lib = load_library("capped")
+    _check(lib.odi_concat_cast(_ptr(a), _ptr(b), _ptr(out), c_long(n), c_int(H), c_int(dtype_code(out.dtype)), _stream()),
+           "concat_cast")
+
+
+def rmsnorm_add(hidden: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """hidden[t] += y[t] * rsqrt(mean(y[t]^2) + eps) * weight, all fp32: the norm of a sublayer's output and the
+    residual add in one pass."""
+    _require(hidden, "hidden", torch.float32, 2)
+    _require(y, "y", torch.float32, 2)
+    _require(weight, "weight", torch.float32, 1)
+    n, H = hidden.shape
+    if y.shape != (n, H) or weight.numel() != H:
+        raise KernelError("rmsnorm_add sizes disagree")
+    lib = load_library("capped")
+    _check(lib.odi_rmsnorm_add(_ptr(hidden), _ptr(y), _ptr(weight), c_int(n), c_int(H), c_float(eps), _stream()), "rmsnorm_add")
+
+
+def gated_row_add(acc: torch.Tensor, y: torch.Tensor, x: torch.Tensor, gate: torch.Tensor) -> None:
+    """acc[t] += sigmoid(x[t] . gate) * y[t]: ``acc`` fp32 [tokens, H], ``y`` fp32 or in the dtype of ``x``,
+    ``x`` [tokens, K] and ``gate`` [K] in the compute dtype; the dot product and the sigmoid in fp32."""
+    _require(acc, "acc", torch.float32, 2)
+    _require(y, "y", ndim=2)
+    _require(x, "x", ndim=2)
+    _require(gate, "gate", x.dtype)
+    n, H = acc.shape
+    if y.shape != (n, H) or x.shape[0] != n or gate.numel() != x.shape[1] or y.dtype not in (torch.float32, x.dtype):
+        raise KernelError("gated_row_add sizes disagree")
+    lib = load_library("capped")
+    _check(lib.odi_gated_row_add(_ptr(acc), _ptr(y), _ptr(x), _ptr(gate), c_int(n), c_int(H), c_int(x.shape[1]),
+                                 c_int(0 if y.dtype == torch.float32 else 1), c_int(dtype_code(x.dtype)), _stream()),
+           "gated_row_add")
 
 
 # ------------------------------------------------------------------------------ the gated delta rule

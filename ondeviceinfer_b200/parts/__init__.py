@@ -1,15 +1,17 @@
 from .base import Part, Runtime, build_part, register_part
 from .linear import gated_linear, linear
-from . import norm, position, attention, mlp, block, embedding, latent_attention, channel_delta, routed_experts  # noqa: F401  (registers the built-in parts)
+from . import norm, position, attention, mlp, block, embedding, latent_attention, channel_delta, routed_experts, capped_attention, table_experts  # noqa: F401  (registers the built-in parts)
 from .attention import Attention
+from .capped_attention import CappedAttention
 from .channel_delta import ChannelDelta
 from .latent_attention import LatentAttention
 from .routed_experts import RoutedExperts
 from .embedding import OutputHead, TokenEmbedding
-from .block import PreNormBlock
-from .mlp import GatedMLP
+from .block import PreNormBlock, Reinject, SandwichBlock
+from .mlp import GatedMLP, PlainMLP
+from .table_experts import TableExperts
 from .norm import RMSNorm
 from .position import NoPosition, Rotary
 
 __all__ = ["Part", "Runtime", "build_part", "register_part", "linear", "gated_linear", "Attention", "PreNormBlock",
-           "GatedMLP", "LatentAttention", "ChannelDelta", "RoutedExperts", "RMSNorm", "NoPosition", "Rotary", "TokenEmbedding", "OutputHead"]
+           "GatedMLP", "PlainMLP", "SandwichBlock", "Reinject", "CappedAttention", "TableExperts", "LatentAttention", "ChannelDelta", "RoutedExperts", "RMSNorm", "NoPosition", "Rotary", "TokenEmbedding", "OutputHead"]

@@ -2,7 +2,10 @@
 
 from __future__ import annotations
 
-from ..config.specs import PreNormBlockSpec
+import torch
+
+from ..config.specs import PreNormBlockSpec, ReinjectSpec, SandwichBlockSpec
+from ..weights.tensors import TensorDecl
 from .base import Part, build_part, register_part
 
 
@@ -70,4 +73,95 @@ class PreNormBlock(Part):
             self.ffn.forward(self._normed(self.ffn_norm, self.ffn, hidden, ctx), ctx, hidden)
 
 
+class SandwichBlock(Part):
+    """h += post_norm(mixer(norm(h))); h += post_norm(feed_forward(norm(h))): a norm on both sides of each sublayer.
+
+    A sublayer's output is taken in fp32, normed in fp32 and added to the fp32 stream in one kernel
+    (``ops.rmsnorm_add``).  A part that says ``returns_output`` (its ``forward`` returns the output when given no residual) is asked for that;
+    any other part adds into a zeroed fp32 buffer, as the part interface says, so every registered mixer and
+    feed-forward fits."""
+
+    def __init__(self, spec: SandwichBlockSpec) -> None:
+        super().__init__(spec)
+        self.mixer_norm = build_part(spec.mixer_norm)
+        self.mixer = build_part(spec.mixer)
+        self.mixer_post_norm = build_part(spec.mixer_post_norm)
+        has = spec.ffn is not None
+        self.ffn_norm = build_part(spec.ffn_norm) if has else None
+        self.ffn = build_part(spec.ffn) if has else None
+        self.ffn_post_norm = build_part(spec.ffn_post_norm) if has else None
+        for norm in (self.mixer_post_norm, self.ffn_post_norm):
+            if norm is not None and not hasattr(norm.spec, "eps"):
+                raise TypeError("the norm after a sublayer must be an RMS norm (a weight and eps)")
+
+    def _children(self):
+        return tuple(part for part in (self.mixer_norm, self.mixer, self.mixer_post_norm, self.ffn_norm, self.ffn,
+                                       self.ffn_post_norm) if part is not None)
+
+    def tensor_decls(self):
+        return [d for part in self._children() for d in part.tensor_decls()]
+
+    def load(self, fetch, runtime) -> None:
+        self.runtime = runtime
+        for part in self._children():
+            part.load(fetch, runtime)
+
+    def cache_needs(self):
+        return tuple(self.mixer.cache_needs())
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(part, "graph_safe", False) for part in self._children())
+
+    @staticmethod
+    def _branch(part, hidden, call):
+        """The fp32 output of a sublayer: ``call(residual)`` runs it."""
+        if getattr(part, "returns_output", False):
+            return call(None)
+        branch = torch.zeros_like(hidden)
+        call(branch)
+        return branch
+
+    def forward(self, hidden, ctx, view) -> None:
+        from ..kernels import ops
+        ctx.defers_residual_add = False
+        out = self._branch(self.mixer, hidden, lambda r: self.mixer.forward(self.mixer_norm(hidden), ctx, view, r))
+        ops.rmsnorm_add(hidden, out, self.mixer_post_norm.weight, self.mixer_post_norm.spec.eps)
+        if self.ffn is not None:
+            out = self._branch(self.ffn, hidden, lambda r: self.ffn.forward(self.ffn_norm(hidden), ctx, r))
+            ops.rmsnorm_add(hidden, out, self.ffn_post_norm.weight, self.ffn_post_norm.spec.eps)
+        ctx.residual_sumsq = None
+
+
+class Reinject(Part):
+    """h <- W [h ; e] + steps[index], e the embedding's output (``ctx.embedded``): what opens a pass of a looped
+    stack.  It keeps no cache and returns the new stream (the model goes on with what a layer returns)."""
+
+    graph_safe = True
+    reads_embedding = True      # the model keeps the embedding's output on the step's context for it
+
+    def tensor_decls(self):
+        s = self.spec
+        return [TensorDecl(s.weight_name, (s.hidden_size, 2 * s.hidden_size)),
+                TensorDecl(s.steps_name, (s.num_steps, s.hidden_size))]
+
+    def load(self, fetch, runtime) -> None:
+        self.runtime = runtime
+        self.weight = fetch.matrix(self.spec.weight_name)
+        self.step = fetch.vector(self.spec.steps_name)[self.spec.index].contiguous()
+
+    def cache_needs(self):
+        return ()
+
+    def forward(self, hidden, ctx, view):
+        from ..kernels import ops
+        from .linear import linear
+        both = torch.empty((hidden.shape[0], 2 * self.spec.hidden_size), dtype=self.runtime.dtype, device=hidden.device)
+        ops.concat_cast(hidden, ctx.embedded, both)
+        ctx.residual_sumsq = None
+        return linear(both, self.weight, bias=self.step, out_dtype=torch.float32)
+
+
 register_part(PreNormBlockSpec, PreNormBlock)
+register_part(SandwichBlockSpec, SandwichBlock)
+register_part(ReinjectSpec, Reinject)

@@ -1,0 +1,106 @@
+"""Grouped-query attention with rotated, unit-normed queries and keys, squashed scores and a window.
+
+Steps of ``forward``: one matrix product for the concatenated q, k, v projections (v heads have a width of their
+own); head preparation (``csrc/capped.cu``): rotation of neighbouring-lane pairs, then every q and k head divided
+by its root mean square, q to the query buffer, k and v to the token's row of the paged cache (a ring of pages
+per sequence when the layer has a window); attention over the cache pages with the scores squashed by
+c tanh(score / c) and keys outside the window left out; the output projection.  Rotation, unit norm, scores and
+softmax are fp32 in both compute dtypes.  Every constant (scale, cap, window, eps, rotated lanes, frequency
+scaling) is a field of the spec; a field that is None switches its mechanism off.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache import PAGE_SIZE, KVNeed
+from ..config.specs import CappedAttentionSpec
+from ..kernels import ops
+from ..weights.tensors import TensorDecl
+from .base import Part, build_part, register_part
+from .linear import linear
+
+
+class CappedAttention(Part):
+    graph_safe = True   # no host work that depends on the step's values: may be captured in a CUDA graph
+    returns_output = True   # forward(..., residual=None) returns the fp32 output instead of adding it
+
+    def __init__(self, spec: CappedAttentionSpec) -> None:
+        super().__init__(spec)
+        if spec.num_heads <= 0 or spec.num_kv_heads <= 0 or spec.num_heads % spec.num_kv_heads != 0:
+            raise ValueError("query heads must be a positive multiple of the key/value heads")
+        if spec.head_dim % 4 != 0 or not 4 <= spec.head_dim <= 512:
+            raise ValueError(f"head_dim={spec.head_dim}: the attention kernels take multiples of 4 up to 512")
+        if spec.value_dim <= 0:
+            raise ValueError("value_dim must be positive")
+        if spec.window is not None and spec.window <= 0:
+            raise ValueError("window must be positive")
+        if spec.softcap is not None and spec.softcap <= 0:
+            raise ValueError("softcap must be positive")
+        self.position = build_part(spec.position)
+        if self.position.rot_dim > 0 and not getattr(self.position, "interleaved", False):
+            raise ValueError("this attention's head preparation rotates neighbouring-lane pairs only")
+
+    # ------------------------------------------------------------------ tensors
+
+    def tensor_decls(self):
+        s = self.spec
+        q, k, v = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim, s.num_kv_heads * s.value_dim
+        return [TensorDecl(s.name("q"), (q, s.hidden_size)), TensorDecl(s.name("k"), (k, s.hidden_size)),
+                TensorDecl(s.name("v"), (v, s.hidden_size)),
+                TensorDecl(s.name("o"), (s.hidden_size, s.num_heads * s.value_dim))] + self.position.tensor_decls()
+
+    def load(self, fetch, runtime) -> None:
+        s = self.spec
+        self.runtime = runtime
+        # q, k and v rows concatenated: one product yields [tokens, nq d + nkv d + nkv dv]
+        self.w_qkv = torch.cat([fetch.matrix(s.name("q")), fetch.matrix(s.name("k")), fetch.matrix(s.name("v"))], 0)
+        self.w_o = fetch.matrix(s.name("o"))
+        self.position.load(fetch, runtime)
+
+    def cache_needs(self):
+        s = self.spec
+        return (KVNeed(s.num_kv_heads, s.head_dim, s.window, value_dim=s.value_dim),)
+
+    # ------------------------------------------------------------------ step
+
+    def forward(self, x, ctx, view, residual):
+        """Adds the mixer's output to ``residual`` (fp32); with ``residual`` None returns it as a new fp32 tensor."""
+        s = self.spec
+        n = x.shape[0]
+        group = view.kv_group
+        page_start, page_ids = ctx.page_table(group.index)
+        tables = self.position.rotary_tables(ctx)
+        cos, sin = tables if tables is not None else (None, None)
+        q = torch.empty((n, s.num_heads * s.head_dim), dtype=x.dtype, device=x.device)
+        ops.rot_unit_prep(linear(x, self.w_qkv), q, view.keys, view.values, cos, sin, ctx.tok_seq, ctx.tok_pos,
+                          page_start, page_ids, nq=s.num_heads, nkv=s.num_kv_heads, d=s.head_dim, dv=s.value_dim,
+                          rot_dim=self.position.rot_dim, page_size=PAGE_SIZE, ring_pages=group.ring_pages,
+                          write_kv=view.writes_kv, unit_eps=s.unit_norm_eps)
+        o = self.attend(q, ctx, view, page_start, page_ids)
+        if residual is None:
+            return linear(o, self.w_o, out_dtype=torch.float32)
+        linear(o, self.w_o, residual=residual, track=ctx)
+        return None
+
+    def attend(self, q, ctx, view, page_start, page_ids):
+        """The attention output [tokens, heads * value_dim]."""
+        s = self.spec
+        o = torch.empty((ctx.n_tokens, s.num_heads * s.value_dim), dtype=q.dtype, device=q.device)
+        splits, partial = 1, None
+        if ctx.max_q_len == 1:
+            # single tokens: cut long key ranges so that enough blocks run side by side
+            block_rows = s.num_kv_heads * ((s.num_heads // s.num_kv_heads + 15) // 16)
+            keys = ctx.max_kv_len if s.window is None else min(ctx.max_kv_len, s.window)
+            splits = max(1, min(32, 296 // max(ctx.n_seqs * block_rows, 1), (keys + 255) // 256))
+            if splits > 1:
+                partial = torch.empty((ctx.n_tokens * s.num_heads * splits * (s.value_dim + 2),), dtype=torch.float32,
+                                      device=q.device)
+        ops.attention_simt(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids, n_seqs=ctx.n_seqs,
+                           max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads, d=s.head_dim, dv=s.value_dim,
+                           page_size=PAGE_SIZE, ring_pages=view.kv_group.ring_pages, window=s.window or 0,
+                           scale=s.scale, splits=splits, partial=partial, softcap=s.softcap or 0.0)
+        return o
+
+
+register_part(CappedAttentionSpec, CappedAttention)

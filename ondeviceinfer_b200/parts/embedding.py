@@ -40,7 +40,7 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
-    """logits = rows W^T in fp32.  A tied head binds the embedding's tensor (the loader hands out one tensor
+    """logits = rows W^T in fp32, squashed by ``softcap`` if the spec has one.  A tied head binds the embedding's tensor (the loader hands out one tensor
     per name, so the table is held once) and declares nothing of its own."""
 
     graph_safe = True
@@ -59,7 +59,10 @@ class OutputHead(Part):
 
     def forward(self, rows: torch.Tensor, ctx) -> torch.Tensor:
         """``rows`` [wanted, hidden] in the compute dtype (already normed) -> fp32 logits [wanted, vocab]."""
-        return linear(rows, self.weight, out_dtype=torch.float32)
+        logits = linear(rows, self.weight, out_dtype=torch.float32)
+        if self.spec.softcap is not None:
+            ops.softcap(logits, self.spec.softcap)        # c tanh(logits / c), in fp32
+        return logits
 
 
 register_part(EmbeddingSpec, TokenEmbedding)

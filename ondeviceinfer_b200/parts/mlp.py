@@ -4,7 +4,8 @@ from __future__ import annotations
 
 import torch
 
-from ..config.specs import GatedMLPSpec
+from ..config.specs import GatedMLPSpec, MLPSpec
+from ..kernels import ops
 from ..weights.tensors import TensorDecl
 from .base import Part, register_part
 from .linear import gated_linear, linear
@@ -38,4 +39,37 @@ class GatedMLP(Part):
         linear(gated_linear(x, self.w_gate_up), self.w_down, residual=residual, track=ctx)
 
 
+class PlainMLP(Part):
+    """down(act(up(x))) without a gate; the activation (the exact GELU or its tanh form) is taken in fp32 on the
+    rounded product and rounded once."""
+
+    graph_safe = True
+    returns_output = True   # forward(..., residual=None) returns the fp32 output instead of adding it
+
+    def __init__(self, spec: MLPSpec) -> None:
+        super().__init__(spec)
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {spec.activation!r} is not implemented ({sorted(ops.ACTIVATIONS)} are)")
+
+    def tensor_decls(self):
+        s = self.spec
+        return [TensorDecl(s.name("up"), (s.intermediate_size, s.hidden_size)),
+                TensorDecl(s.name("down"), (s.hidden_size, s.intermediate_size))]
+
+    def load(self, fetch, runtime) -> None:
+        self.runtime = runtime
+        self.w_up = fetch.matrix(self.spec.name("up"))
+        self.w_down = fetch.matrix(self.spec.name("down"))
+
+    def forward(self, x, ctx, residual):
+        """Adds to ``residual`` (fp32); with ``residual`` None returns the output as a new fp32 tensor."""
+        act = linear(x, self.w_up)
+        ops.activation(act, act, self.spec.activation)
+        if residual is None:
+            return linear(act, self.w_down, out_dtype=torch.float32)
+        linear(act, self.w_down, residual=residual, track=ctx)
+        return None
+
+
 register_part(GatedMLPSpec, GatedMLP)
+register_part(MLPSpec, PlainMLP)

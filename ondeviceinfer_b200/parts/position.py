@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..config.specs import NoPositionSpec, RotarySpec
@@ -9,8 +11,27 @@ from ..kernels import ops
 from .base import Part, register_part
 
 
+def scaled_frequencies(freqs, scaling):
+    """Frequencies with their long wavelengths slowed (``RotarySpec.scaling`` = factor, low, high, original): a
+    wavelength l = 2 pi / f below original / high keeps f, above original / low gets f / factor, and in between
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  Host arithmetic in double."""
+    factor, low, high, original = (float(v) for v in scaling)
+    out = []
+    for f in freqs:
+        wavelength = 2.0 * math.pi / f
+        if wavelength < original / high:
+            out.append(f)
+        elif wavelength > original / low:
+            out.append(f / factor)
+        else:
+            s = (original / wavelength - low) / (high - low)
+            out.append((1.0 - s) * f / factor + s * f)
+    return out
+
+
 class Rotary(Part):
-    """Half-split rotary embedding (ondeviceinfer/layers.py:36-83).
+    """Rotary embedding (ondeviceinfer/layers.py:36-83); which lanes pair up (half-split or neighbours) is the
+    mixer's business, the tables are the same.
 
     ``inv_freq[i] = 1 / theta**(2i / d)`` is evaluated once on the host in fp32 exactly
     as the reference does (ondeviceinfer/layers.py:44-46); angles, cos and sin of a
@@ -27,7 +48,10 @@ class Rotary(Part):
     def load(self, fetch, runtime) -> None:
         self.runtime = runtime
         exponent = torch.arange(0, self.rot_dim, 2, dtype=torch.float32) / self.rot_dim
-        self.inv_freq = (1.0 / (self.spec.theta ** exponent)).to(runtime.device)
+        inv_freq = 1.0 / (self.spec.theta ** exponent)
+        if self.spec.scaling is not None:
+            inv_freq = torch.tensor(scaled_frequencies(inv_freq.double().tolist(), self.spec.scaling), dtype=torch.float32)
+        self.inv_freq = inv_freq.to(runtime.device)
 
     def rotary_tables(self, ctx):
         def make():

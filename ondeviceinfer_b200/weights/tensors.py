@@ -34,7 +34,8 @@ class TensorDecl:
 
     ``init`` is the law of the random-weights mode: ``"normal"`` draws
     normal(0, 0.02), ``"one_plus_normal"`` draws 1 + normal(0, 0.01) (norm weights),
-    ``"zeros"`` is all zero.
+    ``"zeros"`` is all zero, ``"distinct_below:<n>"`` an int32 table whose rows hold distinct
+    values below n.
     """
 
     name: str
@@ -136,13 +137,19 @@ class RandomSource:
         self.std, self.norm_std = std, norm_std
 
     def stored(self) -> Dict[str, StoredTensor]:
-        return {n: StoredTensor(tuple(d.shape), self.dtype) for n, d in self._decls.items()}
+        return {n: StoredTensor(tuple(d.shape), torch.int32 if d.init.startswith("distinct_below:") else self.dtype)
+                for n, d in self._decls.items()}
 
     def fetch(self, name: str) -> torch.Tensor:
         decl = self._decls[name]
         if decl.init == "zeros":
             return torch.zeros(decl.shape, dtype=self.dtype, device=self.device)
         gen = torch.Generator(device=self.device).manual_seed(_name_seed(self.seed, name))
+        if decl.init.startswith("distinct_below:"):
+            # an integer table: every row holds distinct values below the bound, in a random order
+            bound = int(decl.init.split(":")[1])
+            order = torch.rand(tuple(decl.shape[:-1]) + (bound,), generator=gen, device=self.device).argsort(-1)
+            return order[..., :decl.shape[-1]].to(torch.int32).contiguous()
         t = torch.randn(decl.shape, generator=gen, dtype=torch.float32, device=self.device)
         if decl.init == "one_plus_normal":
             t.mul_(self.norm_std).add_(1.0)
