@@ -14,8 +14,8 @@
 
 struct RotUnitArgs {
   const void* qkv;      // [n_tokens, nq * d + nkv * d + nkv * dv]
-  void* q_out;          // [n_tokens, nq * d]
-  void* k_pool;         // [pages, nkv, page_size, d]
+  void* q_out;          // [n_tokens, nq * d_store]
+  void* k_pool;         // [pages, nkv, page_size, d_store]
   void* v_pool;         // [pages, nkv, page_size, dv]
   const float* cos_t;   // null: no rotation; [n_tokens, rot_dim / 2]
   const float* sin_t;
@@ -24,6 +24,7 @@ struct RotUnitArgs {
   const int* page_start;
   const int* page_ids;
   int n_tokens, nq, nkv, d, dv, rot_dim, page_size, ring_pages, write_kv, unit;
+  int d_store;          // lanes of a stored q or k head, >= d; the lanes beyond d are written as zero
   float eps;
 };
 
@@ -46,7 +47,7 @@ __global__ void rot_unit_prep_kernel(RotUnitArgs a) {
   T* dst;
   if (kind == 0) {
     src = (const T*)a.qkv + (size_t)t * row + (size_t)h * d;
-    dst = (T*)a.q_out + ((size_t)t * a.nq + h) * d;
+    dst = (T*)a.q_out + ((size_t)t * a.nq + h) * a.d_store;
   } else {
     const int hk = kind == 1 ? h - a.nq : h - a.nq - a.nkv;
     const int s = a.tok_seq[t];
@@ -54,7 +55,7 @@ __global__ void rot_unit_prep_kernel(RotUnitArgs a) {
     const size_t at = ((size_t)page * a.nkv + hk) * a.page_size + (pos % a.page_size);
     if (kind == 1) {
       src = (const T*)a.qkv + (size_t)t * row + (size_t)(a.nq + hk) * d;
-      dst = (T*)a.k_pool + at * d;
+      dst = (T*)a.k_pool + at * a.d_store;
     } else {
       src = (const T*)a.qkv + (size_t)t * row + (size_t)(a.nq + a.nkv) * d + (size_t)hk * a.dv;
       dst = (T*)a.v_pool + at * a.dv;
@@ -93,22 +94,22 @@ __global__ void rot_unit_prep_kernel(RotUnitArgs a) {
 #pragma unroll
   for (int r = 0; r < MAXP; ++r) {
     const int i = lane + 32 * r;
-    if (i < d) dst[i] = from_f<T>(x[r]);
+    if (i < a.d_store) dst[i] = from_f<T>(i < d ? x[r] : 0.f);
   }
 }
 
 extern "C" int odi_rot_unit_prep(const RotUnitArgs* args, int dtype, cudaStream_t stream) {
   RotUnitArgs a = *args;
   if (a.n_tokens <= 0) return 0;
-  if (a.d > 512 || a.d <= 0 || a.dv <= 0 || (a.rot_dim & 1) || a.rot_dim > a.d) return ODI_ERR_UNSUPPORTED;
+  if (a.d_store > 512 || a.d <= 0 || a.d_store < a.d || a.dv <= 0 || (a.rot_dim & 1) || a.rot_dim > a.d) return ODI_ERR_UNSUPPORTED;
   const int heads = a.nq + (a.write_kv ? 2 * a.nkv : 0);
   const long items = (long)a.n_tokens * heads;
   const int blocks = (int)((items + 3) / 4);
 #define ODI_LAUNCH(T, P) odi_rc = launch_pdl((rot_unit_prep_kernel<T, P>), dim3(blocks), dim3(128), 0, stream, a)
   if (dtype == 0) {
-    if (a.d <= 128) ODI_LAUNCH(float, 4); else if (a.d <= 256) ODI_LAUNCH(float, 8); else ODI_LAUNCH(float, 16);
+    if (a.d_store <= 128) ODI_LAUNCH(float, 4); else if (a.d_store <= 256) ODI_LAUNCH(float, 8); else ODI_LAUNCH(float, 16);
   } else {
-    if (a.d <= 128) ODI_LAUNCH(bf16, 4); else if (a.d <= 256) ODI_LAUNCH(bf16, 8); else ODI_LAUNCH(bf16, 16);
+    if (a.d_store <= 128) ODI_LAUNCH(bf16, 4); else if (a.d_store <= 256) ODI_LAUNCH(bf16, 8); else ODI_LAUNCH(bf16, 16);
   }
 #undef ODI_LAUNCH
   return launch_status();

@@ -1140,26 +1140,28 @@ class _RotUnitArgs(Structure):
                 ("cos_t", c_void_p), ("sin_t", c_void_p), ("tok_seq", c_void_p), ("tok_pos", c_void_p),
                 ("page_start", c_void_p), ("page_ids", c_void_p), ("n_tokens", c_int), ("nq", c_int), ("nkv", c_int),
                 ("d", c_int), ("dv", c_int), ("rot_dim", c_int), ("page_size", c_int), ("ring_pages", c_int),
-                ("write_kv", c_int), ("unit", c_int), ("eps", c_float)]
+                ("write_kv", c_int), ("unit", c_int), ("d_store", c_int), ("eps", c_float)]
 
 
 def rot_unit_prep(qkv, q_out, k_pool, v_pool, cos_t, sin_t, tok_seq, tok_pos, page_start, page_ids, *, nq: int,
                   nkv: int, d: int, dv: int, rot_dim: int, page_size: int, ring_pages: int, write_kv: bool,
-                  unit_eps: Optional[float]) -> None:
+                  unit_eps: Optional[float], d_store: Optional[int] = None) -> None:
     """Head preparation of an attention that rotates first and norms afterwards: q and k heads (``d`` lanes) of
     ``qkv`` [tokens, nq d + nkv d + nkv dv] are rotated over their first ``rot_dim`` lanes (lane 2i with 2i + 1;
     ``cos_t`` None: not at all) and, with ``unit_eps`` not None, divided by sqrt(mean of squares + eps); q goes to
-    ``q_out``, k and the v heads (``dv`` lanes, as they are) to the token's row of their cache pages."""
+    ``q_out``, k and the v heads (``dv`` lanes, as they are) to the token's row of their cache pages.  Stored q
+    and k heads have ``d_store`` >= ``d`` lanes (default ``d``), the ones beyond ``d`` zero."""
+    d_store = d if d_store is None else d_store
     _require(qkv, "qkv", ndim=2)
     _require(q_out, "q_out", qkv.dtype, 2)
     n = qkv.shape[0]
-    if qkv.shape[1] != (nq + nkv) * d + nkv * dv or q_out.shape != (n, nq * d):
+    if qkv.shape[1] != (nq + nkv) * d + nkv * dv or q_out.shape != (n, nq * d_store):
         raise KernelError(f"rot_unit_prep sizes disagree: qkv {tuple(qkv.shape)}, q_out {tuple(q_out.shape)}, "
                           f"nq={nq}, nkv={nkv}, d={d}, dv={dv}")
     if write_kv:
         _require(k_pool, "k_pool", qkv.dtype)
         _require(v_pool, "v_pool", qkv.dtype)
-        if k_pool.shape[-1] != d or v_pool.shape[-1] != dv:
+        if k_pool.shape[-1] != d_store or v_pool.shape[-1] != dv:
             raise KernelError("the cache pools do not have the heads' widths")
     if cos_t is not None:
         _require(cos_t, "cos_t", torch.float32, 2)
@@ -1168,7 +1170,7 @@ def rot_unit_prep(qkv, q_out, k_pool, v_pool, cos_t, sin_t, tok_seq, tok_pos, pa
             raise KernelError("rope tables must be [tokens, rot_dim / 2]")
     args = _RotUnitArgs(_ptr(qkv), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(cos_t), _ptr(sin_t), _ptr(tok_seq),
                         _ptr(tok_pos), _ptr(page_start), _ptr(page_ids), n, nq, nkv, d, dv, rot_dim, page_size, ring_pages,
-                        1 if write_kv else 0, 0 if unit_eps is None else 1, 0.0 if unit_eps is None else unit_eps)
+                        1 if write_kv else 0, 0 if unit_eps is None else 1, d_store, 0.0 if unit_eps is None else unit_eps)
     lib = load_library("capped")
     _check(lib.odi_rot_unit_prep(byref(args), c_int(dtype_code(qkv.dtype)), _stream()), "rot_unit_prep")
 

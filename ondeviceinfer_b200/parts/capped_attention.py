@@ -29,8 +29,10 @@ class CappedAttention(Part):
         super().__init__(spec)
         if spec.num_heads <= 0 or spec.num_kv_heads <= 0 or spec.num_heads % spec.num_kv_heads != 0:
             raise ValueError("query heads must be a positive multiple of the key/value heads")
-        if spec.head_dim % 4 != 0 or not 4 <= spec.head_dim <= 512:
-            raise ValueError(f"head_dim={spec.head_dim}: the attention kernels take multiples of 4 up to 512")
+        if not 1 <= spec.head_dim <= 512:
+            raise ValueError(f"head_dim={spec.head_dim}: the attention kernels take heads of up to 512 lanes")
+        # the attention kernel reads heads four lanes at a time: stored q and k heads are padded with zero lanes
+        self.lanes = -(-spec.head_dim // 4) * 4
         if spec.value_dim <= 0:
             raise ValueError("value_dim must be positive")
         if spec.window is not None and spec.window <= 0:
@@ -60,7 +62,7 @@ class CappedAttention(Part):
 
     def cache_needs(self):
         s = self.spec
-        return (KVNeed(s.num_kv_heads, s.head_dim, s.window, value_dim=s.value_dim),)
+        return (KVNeed(s.num_kv_heads, self.lanes, s.window, value_dim=s.value_dim),)
 
     # ------------------------------------------------------------------ step
 
@@ -72,11 +74,11 @@ class CappedAttention(Part):
         page_start, page_ids = ctx.page_table(group.index)
         tables = self.position.rotary_tables(ctx)
         cos, sin = tables if tables is not None else (None, None)
-        q = torch.empty((n, s.num_heads * s.head_dim), dtype=x.dtype, device=x.device)
+        q = torch.empty((n, s.num_heads * self.lanes), dtype=x.dtype, device=x.device)
         ops.rot_unit_prep(linear(x, self.w_qkv), q, view.keys, view.values, cos, sin, ctx.tok_seq, ctx.tok_pos,
                           page_start, page_ids, nq=s.num_heads, nkv=s.num_kv_heads, d=s.head_dim, dv=s.value_dim,
                           rot_dim=self.position.rot_dim, page_size=PAGE_SIZE, ring_pages=group.ring_pages,
-                          write_kv=view.writes_kv, unit_eps=s.unit_norm_eps)
+                          write_kv=view.writes_kv, unit_eps=s.unit_norm_eps, d_store=self.lanes)
         o = self.attend(q, ctx, view, page_start, page_ids)
         if residual is None:
             return linear(o, self.w_o, out_dtype=torch.float32)
@@ -97,7 +99,7 @@ class CappedAttention(Part):
                 partial = torch.empty((ctx.n_tokens * s.num_heads * splits * (s.value_dim + 2),), dtype=torch.float32,
                                       device=q.device)
         ops.attention_simt(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids, n_seqs=ctx.n_seqs,
-                           max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads, d=s.head_dim, dv=s.value_dim,
+                           max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads, d=self.lanes, dv=s.value_dim,
                            page_size=PAGE_SIZE, ring_pages=view.kv_group.ring_pages, window=s.window or 0,
                            scale=s.scale, splits=splits, partial=partial, softcap=s.softcap or 0.0)
         return o

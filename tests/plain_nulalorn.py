@@ -168,3 +168,170 @@ def forward(config, tensors, token_ids, positions=None):
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return logits, torch.stack(streams)
+
+
+# ------------------------------------------------------------------------------ small models for the tests
+
+
+def attention_layer(*, heads, kv_heads, dim, vdim, scale, softcap=None, window=None, rot=None, mlp=None):
+    mixer = {"dim": dim, "heads": heads, "kv_heads": kv_heads, "scale": scale, "vdim": vdim}
+    if softcap is not None:
+        mixer["softcap"] = softcap
+    if window is not None:
+        mixer["mask"] = {"size": window}
+    if rot is not None:
+        mixer["rot"] = rot
+    return {"type": "attention", "mixer": mixer, "mlp": mlp}
+
+
+def moe(experts, top, ff, shared=None):
+    f = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    if shared is not None:
+        f["shared"] = {"ff": shared}
+    return f
+
+
+SCALED = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}      # at base 100, 8 lanes: keep, blend, blend, slow
+
+# A: a dense layer, then two layers with experts that run three times, then a layer without feed-forward.
+TINY_A = {
+    "architecture": "Nulalorn", "vocab": 61, "width": 48, "norm": {"eps": 1e-5}, "logit_softcap": 12.0,
+    "loop": {"start": 1, "stop": 3, "times": 3},
+    "layers": [
+        attention_layer(heads=4, kv_heads=2, dim=16, vdim=8, scale=0.4, softcap=9.0, window=7,
+                        rot={"base": 100.0, "dims": 8, "scaling": SCALED}, mlp={"kind": "dense", "ff": 72}),
+        attention_layer(heads=4, kv_heads=2, dim=16, vdim=8, scale=0.4, softcap=9.0, window=7,
+                        rot={"base": 100.0, "dims": 8, "scaling": SCALED}, mlp=moe(5, 2, 24, shared=40)),
+        attention_layer(heads=2, kv_heads=1, dim=32, vdim=24, scale=0.25, softcap=5.0, window=70,
+                        rot={"base": 1000.0, "dims": 32}, mlp=moe(3, 1, 32)),
+        attention_layer(heads=4, kv_heads=4, dim=16, vdim=16, scale=0.3, window=3, rot={"base": 50.0, "dims": 2}),
+    ],
+}
+
+# B: values that may be one or equal elsewhere are not here: every head its own key/value head, a value as wide as
+# a key, one expert per token, the loop from the first layer on, a layer that sees every key, no cap on the logits.
+TINY_B = {
+    "architecture": "Nulalorn", "vocab": 45, "width": 40, "norm": {"eps": 1e-6},
+    "loop": {"start": 0, "stop": 1, "times": 2},
+    "layers": [
+        attention_layer(heads=3, kv_heads=3, dim=12, vdim=12, scale=0.5, rot={"base": 300.0, "dims": 12},
+                        mlp=moe(4, 1, 16, shared=8)),
+        attention_layer(heads=5, kv_heads=1, dim=8, vdim=20, scale=0.6, softcap=4.0, window=64, mlp={"kind": "dense", "ff": 56}),
+    ],
+}
+
+# C: odd sizes: a width off the multiples of 8, heads of 6 lanes (stored as 8), values of 5, six query heads on one
+# key/value head, a window of one (a token sees itself only), three experts of five, a loop over all layers, run once.
+TINY_C = {
+    "architecture": "Nulalorn", "vocab": 33, "width": 44, "norm": {"eps": 1e-4}, "logit_softcap": 3.0,
+    "loop": {"start": 0, "stop": 2, "times": 1},
+    "layers": [
+        attention_layer(heads=6, kv_heads=1, dim=6, vdim=5, scale=0.9, softcap=2.5, window=1,
+                        rot={"base": 10.0, "dims": 6, "scaling": {"factor": 2.0, "low": 1.0, "high": 2.0, "original": 16}},
+                        mlp=moe(5, 3, 12, shared=20)),
+        attention_layer(heads=2, kv_heads=2, dim=20, vdim=4, scale=0.35, softcap=30.0, window=130,
+                        rot={"base": 10000.0, "dims": 4}, mlp={"kind": "dense", "ff": 30}),
+    ],
+}
+
+# SHARP: one looped layer whose scores reach scale * dim = 24 before a cap of 40: the softmax picks single keys
+# anywhere inside a window of 300 positions (several pages), so a lost or misplaced far key moves the logits.
+SHARP = {
+    "architecture": "Nulalorn", "vocab": 50, "width": 32, "norm": {"eps": 1e-5}, "logit_softcap": 20.0,
+    "loop": {"start": 0, "stop": 1, "times": 2},
+    "layers": [attention_layer(heads=2, kv_heads=1, dim=16, vdim=16, scale=1.5, softcap=40.0, window=300,
+                               rot={"base": 10000.0, "dims": 8}, mlp={"kind": "dense", "ff": 48})],
+}
+
+# NOLOOP: no loop at all and nothing optional.
+PLAIN_STACK = {
+    "architecture": "Nulalorn", "vocab": 29, "width": 24, "norm": {"eps": 1e-5},
+    "layers": [attention_layer(heads=2, kv_heads=2, dim=8, vdim=8, scale=0.35, mlp={"kind": "dense", "ff": 40}),
+               attention_layer(heads=1, kv_heads=1, dim=16, vdim=12, scale=0.25, window=9, mlp=moe(2, 2, 8))],
+}
+
+
+def tensor_shapes(config):
+    """name -> shape of every tensor the design stores for ``config`` (an integer table: rows, entries per row, bound, 'int')."""
+    D, V = config["width"], config["vocab"]
+    shapes = {"embed": (V, D), "final.norm": (D,), "head": (V, D)}
+    if config.get("loop"):
+        shapes["loop.in"] = (D, 2 * D)
+        shapes["loop.step"] = (config["loop"]["times"], D)
+    for i, entry in enumerate(config["layers"]):
+        p, m = f"l{i}.", entry["mixer"]
+        shapes[p + "norm1"] = shapes[p + "norm1b"] = (D,)
+        shapes[p + "mix.q"] = (m["heads"] * m["dim"], D)
+        shapes[p + "mix.k"] = (m["kv_heads"] * m["dim"], D)
+        shapes[p + "mix.v"] = (m["kv_heads"] * m["vdim"], D)
+        shapes[p + "mix.o"] = (D, m["heads"] * m["vdim"])
+        f = entry.get("mlp")
+        if f is None:
+            continue
+        shapes[p + "norm2"] = shapes[p + "norm2b"] = (D,)
+        if f["kind"] == "dense":
+            shapes[p + "mlp.up"], shapes[p + "mlp.down"] = (f["ff"], D), (D, f["ff"])
+            continue
+        for e in range(f["router"]["experts"]):
+            shapes[f"{p}mlp.e{e}.up"], shapes[f"{p}mlp.e{e}.down"] = (f["expert"]["ff"], D), (D, f["expert"]["ff"])
+        shapes[p + "mlp.table"] = (V, f["router"]["top"], f["router"]["experts"], "int")
+        if f.get("shared"):
+            shapes[p + "mlp.shared.up"], shapes[p + "mlp.shared.down"] = (f["shared"]["ff"], D), (D, f["shared"]["ff"])
+            shapes[p + "mlp.shared.sg"] = (1, D)
+    return shapes
+
+
+def random_weights(config, seed):
+    """Tensors as a checkpoint stores them (bfloat16, tables int32): matrices normal with a spread that keeps every
+    activation of order one, norm weights around one, a table of distinct experts per token id."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(config).items():
+        if shape[-1] == "int":
+            rows = [torch.randperm(shape[2], generator=g)[:shape[1]] for _ in range(shape[0])]
+            out[name] = torch.stack(rows).to(torch.int32)
+        elif len(shape) == 1:
+            out[name] = (1.0 + 0.2 * torch.randn(shape, generator=g)).to(torch.bfloat16)
+        elif name in ("embed", "loop.step"):
+            out[name] = torch.randn(shape, generator=g).to(torch.bfloat16)
+        else:
+            out[name] = (torch.randn(shape, generator=g) * (1.5 / shape[-1] ** 0.5)).to(torch.bfloat16)
+    return out
+
+
+def random_prompts(config, lengths, seed):
+    g = torch.Generator().manual_seed(1000 + seed)
+    return [torch.randint(0, config["vocab"], (n,), generator=g).tolist() for n in lengths]
+
+
+def random_config(seed):
+    """A configuration drawn from odd values: sizes, counts, windows, loop and optional mechanisms all vary."""
+    g = torch.Generator().manual_seed(500 + seed)
+    pick = lambda *values: values[int(torch.randint(0, len(values), (1,), generator=g))]
+    width, vocab = pick(20, 36, 52, 64), pick(17, 40, 75)
+    layers = []
+    for _ in range(pick(1, 2, 3)):
+        kv = pick(1, 2, 3)
+        dim, half = pick(4, 10, 16, 24, 36), None
+        rot = None
+        if pick(True, True, False):
+            rot = {"base": pick(10.0, 500.0, 10000.0), "dims": pick(2, 4, dim)}
+            if pick(True, False):
+                rot["scaling"] = {"factor": pick(2.0, 4.0), "low": 1.0, "high": pick(2.0, 4.0), "original": pick(8, 64, 512)}
+        kind = pick("dense", "moe", "moe", None)
+        mlp = None
+        if kind == "dense":
+            mlp = {"kind": "dense", "ff": pick(8, 28, 72)}
+        elif kind == "moe":
+            experts = pick(1, 2, 6, 9)
+            mlp = moe(experts, pick(*range(1, min(experts, 3) + 1)), pick(8, 12, 40), shared=pick(None, 8, 24))
+        layers.append(attention_layer(heads=kv * pick(1, 2, 4), kv_heads=kv, dim=dim, vdim=pick(3, 8, dim, 40),
+                                      scale=pick(0.2, 0.5, 1.0) / dim ** 0.5 * 2, softcap=pick(None, 3.0, 25.0),
+                                      window=pick(None, 1, 2, 33, 64, 65, 100), rot=rot, mlp=mlp))
+    config = {"architecture": "Nulalorn", "vocab": vocab, "width": width, "norm": {"eps": pick(1e-6, 1e-5, 1e-3)}, "layers": layers}
+    if pick(True, True, False):
+        start = pick(*range(len(layers)))
+        config["loop"] = {"start": start, "stop": pick(*range(start + 1, len(layers) + 1)), "times": pick(1, 2, 3)}
+    if pick(True, False):
+        config["logit_softcap"] = pick(2.0, 30.0)
+    return config
