@@ -34,7 +34,7 @@ lengths and with temperature sampling.  One JSON line is printed:
 on the same configuration, and prints the same line with ``"impl": "reference"``.  Nothing of
 this library is imported in that arm.
 
-``--design lemesun`` leaves the default workload alone and measures the second architecture instead: prefill and
+``--design lemesun`` (or ``nulalorn``) leaves the default workload alone and measures that architecture instead: prefill and
 decode throughput at layer sizes like a real model's beside the dense model of equal width, one JSON line
 (``run_design_points``).
 
@@ -604,7 +604,26 @@ def _dense_config(width, heads, intermediate, layers, vocab):
                 num_key_value_heads=max(1, heads // 4), head_dim=128, intermediate_size=intermediate, vocab_size=vocab)
 
 
+def _nulalorn_config(width, heads, kv_heads, dim, vdim, window, experts, top, ff, shared_ff, dense_ff, vocab):
+    """A dense layer, then three layers with table-routed experts that run twice: seven executions."""
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "softcap": 50.0,
+             "mask": {"size": window},
+             "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    moe = {"kind": "moe", "expert": {"ff": ff}, "shared": {"ff": shared_ff}, "router": {"experts": experts, "top": top}}
+    layer = lambda mlp: {"type": "attention", "mixer": mixer, "mlp": mlp}
+    return {"architecture": "Nulalorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "loop": {"start": 1, "stop": 4, "times": 2},
+            "layers": [layer({"kind": "dense", "ff": dense_ff})] + [layer(moe) for _ in range(3)]}
+
+
 # name -> (the design's configuration, the dense model of equal width and equal active feed-forward width)
+NULALORN_POINTS = {
+    "w2048": (_nulalorn_config(2048, 16, 4, 128, 128, 1024, 32, 4, 1024, 1024, 5 * 1024, 32768),
+              _dense_config(2048, 16, 5 * 1024, 7, 32768)),
+    "w4096": (_nulalorn_config(4096, 32, 8, 128, 128, 1024, 64, 6, 1536, 3072, 6 * 1536 + 3072, 32768),
+              _dense_config(4096, 32, 6 * 1536 + 3072, 7, 32768)),
+}
+
 DESIGN_POINTS = {
     "w2048": (_lemesun_config(2048, 16, 64, 32, 64, 256, 30, 2, 4, 2, 4, 1024, 1024, 4, 32768),
               _dense_config(2048, 16, 5 * 1024, 4, 32768)),
@@ -617,7 +636,7 @@ def _time_parts(model, cache, slots, runs, torch):
     """Device time of every mixer and feed-forward call of one step, by part class: {name: [us, calls]}."""
     events, restore = [], []
     for block in model.decoder.layers:
-        for part in (block.mixer, block.ffn):
+        for part in (getattr(block, "mixer", None), getattr(block, "ffn", None)):
             if part is None:
                 continue
             original = part.forward
@@ -646,9 +665,10 @@ def _time_parts(model, cache, slots, runs, torch):
 
 
 def run_design_points(args) -> int:
-    """``--design lemesun``: prefill and decode throughput of the Lemesun design at layer sizes like a real model's
-    (random weights), each beside the dense Qwen3 model of equal width, heads and active feed-forward width, with
-    the device time of every mixer and feed-forward call.  One JSON line; the default workload is untouched."""
+    """``--design lemesun|nulalorn``: prefill and decode throughput of that design at layer sizes like a real model's
+    (random weights), each beside the dense Qwen3 model of equal width, heads, layer executions and active
+    feed-forward width, with the device time of every mixer and feed-forward call.  One JSON line; the default
+    workload is untouched."""
     import torch
 
     import ondeviceinfer_b200 as odi
@@ -663,13 +683,14 @@ def run_design_points(args) -> int:
     points = {}
     sampler = ClockSampler()
     sampler.start()
-    for name, configs in DESIGN_POINTS.items():
+    design_points = NULALORN_POINTS if args.design == "nulalorn" else DESIGN_POINTS
+    for name, configs in design_points.items():
         if args.design_points and name not in args.design_points.split(","):
             continue
-        for label, cfg in zip(("lemesun", "dense"), configs):
+        for label, cfg in zip((args.design, "dense"), configs):
             model = odi.random_resident_model(cfg, args.seed, dtype="bfloat16")
             vocab = model.vocab_size
-            cache = model.make_cache(max_tokens=batch * (prompt + steps + 64 + 64), max_seqs=batch)
+            cache = model.make_cache(max_tokens=batch * (prompt + steps + 64 + 64), max_seqs=batch, max_step_tokens=prompt)
             ids = torch.randint(0, vocab, (batch, prompt), generator=gen).tolist()
             # prefill of one prompt: warm-up, then the median of three, each on an empty slot
             times = []
@@ -705,11 +726,11 @@ def run_design_points(args) -> int:
             del model, cache
             torch.cuda.empty_cache()
     clocks = sampler.stop()
-    print(json.dumps({"metric": "prefill and decode tokens/s of the Lemesun design beside the dense model of equal size",
+    print(json.dumps({"metric": f"prefill and decode tokens/s of the {args.design.capitalize()} design beside the dense model of equal size",
                       "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "impl": "ours", "higher_is_better": True,
                       "data": "synthetic: seeded random weights, uniform random token ids",
-                      "config": {"prompt_len": prompt, "global_batch": batch, "decode_steps": steps, "layers": 4,
-                                 "peaks": peak_source, "points": {k: {"lemesun": v[0], "dense": v[1]} for k, v in DESIGN_POINTS.items()
+                      "config": {"prompt_len": prompt, "global_batch": batch, "decode_steps": steps, "layers": 7 if args.design == "nulalorn" else 4,
+                                 "peaks": peak_source, "points": {k: {args.design: v[0], "dense": v[1]} for k, v in design_points.items()
                                                                   if k in points}},
                       "peaks": peaks, "points": points, "clocks": clocks}))
     return 0
@@ -747,7 +768,7 @@ def main() -> int:
     parser.add_argument("--prompt-range", default=None, metavar="LOW,HIGH",
                         help="unequal prompts: lengths uniform in [LOW, HIGH] from --seed instead of --prompt-len")
     parser.add_argument("--context", type=int, default=None, help="cache positions per sequence (default 4096, or what the prompt needs)")
-    parser.add_argument("--design", default=None, choices=["lemesun"],
+    parser.add_argument("--design", default=None, choices=["lemesun", "nulalorn"],
                         help="instead of the default workload: this design at real layer sizes beside the dense model of equal size")
     parser.add_argument("--design-points", default=None, help="which of the design's sizes, with commas (default: all)")
     args = parser.parse_args()

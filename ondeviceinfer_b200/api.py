@@ -59,12 +59,17 @@ class ResidentModel:
     def vocab_size(self) -> int:
         return self.decoder.vocab_size
 
-    def make_cache(self, *, max_tokens: int, max_seqs: Optional[int] = None) -> SequenceCache:
+    def make_cache(self, *, max_tokens: int, max_seqs: Optional[int] = None,
+                   max_step_tokens: Optional[int] = None) -> SequenceCache:
         """A cache for at most ``max_tokens`` tokens held by live sequences (each sequence
-        rounded up to pages of 64) and at most ``max_seqs`` sequences at a time."""
+        rounded up to pages of 64) and at most ``max_seqs`` sequences at a time.  ``max_step_tokens``: for
+        layers with a window, the most tokens of a sequence that one pass over the layers takes (longer
+        portions are cut); a sequence then keeps at most window + that many positions."""
         if max_seqs is None:
             max_seqs = max(1, pages_for(max_tokens))
-        return self.decoder.make_cache(max_tokens=max_tokens, max_seqs=max_seqs)
+        if max_step_tokens is None:
+            return self.decoder.make_cache(max_tokens=max_tokens, max_seqs=max_seqs)
+        return self.decoder.make_cache(max_tokens=max_tokens, max_seqs=max_seqs, max_step_tokens=max_step_tokens)
 
     def make_resident_cache(self, *, batch_size: int, max_seq_len: int) -> SequenceCache:
         if max_seq_len <= 0:

@@ -132,11 +132,31 @@ __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, 
   out[i] = from_f<T>(kind == 0 ? gelu_erf(z) : gelu_tanh(z));
 }
 
+// Eight bf16 per thread (16-byte loads and stores); n8 = n / 8.
+__global__ void activation_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, long n8, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  uint4 raw = x[i];
+  __nv_bfloat162* h = (__nv_bfloat162*)&raw;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(h[e]);
+    h[e] = kind == 0 ? __floats2bfloat162_rn(gelu_erf(f.x), gelu_erf(f.y)) : __floats2bfloat162_rn(gelu_tanh(f.x), gelu_tanh(f.y));
+  }
+  out[i] = raw;
+}
+
 // kind: 0 the exact (erf) GELU, 1 its tanh form
 extern "C" int odi_activation(const void* x, void* out, long n, int kind, int dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (kind < 0 || kind > 1) return ODI_ERR_ARGUMENT;
   const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == 1 && n % 8 == 0 && ((uintptr_t)x | (uintptr_t)out) % 16 == 0) {
+    odi_rc = launch_pdl((activation_vec_kernel), dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, stream, (const uint4*)x, (uint4*)out, n / 8, kind);
+    return launch_status();
+  }
   if (dtype == 0) odi_rc = launch_pdl((activation_kernel<float>), dim3(blocks), dim3(256), 0, stream, (const float*)x, (float*)out, n, kind);
   else odi_rc = launch_pdl((activation_kernel<bf16>), dim3(blocks), dim3(256), 0, stream, (const bf16*)x, (bf16*)out, n, kind);
   return launch_status();
@@ -168,9 +188,36 @@ __global__ void concat_cast_kernel(const float* __restrict__ a, const float* __r
   out[i] = from_f<T>(c < H ? a[t * H + c] : b[t * H + c - H]);
 }
 
+// Four elements per thread (H a multiple of 4, so the four come from one source); n4 = rows * 2 H / 4.
+template <typename T>
+__global__ void concat_cast_vec_kernel(const float4* __restrict__ a, const float4* __restrict__ b, T* __restrict__ out,
+                                       long n4, int H4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  const long t = i / (2 * H4);
+  const int c = (int)(i % (2 * H4));
+  const float4 v = c < H4 ? a[t * H4 + c] : b[t * H4 + c - H4];
+  if (sizeof(T) == 4) {
+    ((float4*)out)[i] = v;
+  } else {
+    uint2 packed;
+    *(__nv_bfloat162*)&packed.x = __floats2bfloat162_rn(v.x, v.y);
+    *(__nv_bfloat162*)&packed.y = __floats2bfloat162_rn(v.z, v.w);
+    ((uint2*)out)[i] = packed;
+  }
+}
+
 extern "C" int odi_concat_cast(const float* a, const float* b, void* out, long rows, int H, int dtype, cudaStream_t stream) {
   const long n = rows * 2 * H;
   if (n <= 0) return 0;
+  if (H % 4 == 0 && ((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) % 16 == 0) {
+    const unsigned vblocks = (unsigned)((n / 4 + 255) / 256);
+    if (dtype == 0) odi_rc = launch_pdl((concat_cast_vec_kernel<float>), dim3(vblocks), dim3(256), 0, stream, (const float4*)a, (const float4*)b, (float*)out, n / 4, H / 4);
+    else odi_rc = launch_pdl((concat_cast_vec_kernel<bf16>), dim3(vblocks), dim3(256), 0, stream, (const float4*)a, (const float4*)b, (bf16*)out, n / 4, H / 4);
+    return launch_status();
+  }
   const unsigned blocks = (unsigned)((n + 255) / 256);
   if (dtype == 0) odi_rc = launch_pdl((concat_cast_kernel<float>), dim3(blocks), dim3(256), 0, stream, a, b, (float*)out, n, H);
   else odi_rc = launch_pdl((concat_cast_kernel<bf16>), dim3(blocks), dim3(256), 0, stream, a, b, (bf16*)out, n, H);
@@ -191,8 +238,62 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ hidden, const float* __re
   for (int i = threadIdx.x; i < H; i += blockDim.x) hidden[base + i] += y[base + i] * inv * w[i];
 }
 
+// The same with 16-byte accesses (H a multiple of 4); the row of y stays in registers between the two passes when
+// NV float4 per thread cover it (NV = 0: it is read again).
+template <int NV>
+__global__ void rmsnorm_add_vec_kernel(float4* __restrict__ hidden, const float4* __restrict__ y, const float4* __restrict__ w,
+                                       int H4, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const size_t base = (size_t)blockIdx.x * H4;
+  float4 keep[NV > 0 ? NV : 1];
+  float ss = 0.f;
+  if (NV > 0) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      keep[j] = i < H4 ? y[base + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      ss += keep[j].x * keep[j].x + keep[j].y * keep[j].y + keep[j].z * keep[j].z + keep[j].w * keep[j].w;
+    }
+  } else {
+    for (int i = threadIdx.x; i < H4; i += blockDim.x) { const float4 v = y[base + i]; ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)(4 * H4) + eps);
+  if (NV > 0) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < H4) {
+        float4 h = hidden[base + i];
+        const float4 g = w[i];
+        h.x += keep[j].x * inv * g.x; h.y += keep[j].y * inv * g.y; h.z += keep[j].z * inv * g.z; h.w += keep[j].w * inv * g.w;
+        hidden[base + i] = h;
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < H4; i += blockDim.x) {
+      float4 h = hidden[base + i];
+      const float4 v = y[base + i], g = w[i];
+      h.x += v.x * inv * g.x; h.y += v.y * inv * g.y; h.z += v.z * inv * g.z; h.w += v.w * inv * g.w;
+      hidden[base + i] = h;
+    }
+  }
+}
+
 extern "C" int odi_rmsnorm_add(float* hidden, const float* y, const float* w, int n, int H, float eps, cudaStream_t stream) {
   if (n <= 0) return 0;
+  if (H % 4 == 0 && ((uintptr_t)hidden | (uintptr_t)y | (uintptr_t)w) % 16 == 0) {
+    const int H4 = H / 4;
+    const int vthreads = H4 >= 1024 ? 512 : (H4 >= 256 ? 256 : (H4 >= 128 ? 128 : 64));
+    const int per = (H4 + vthreads - 1) / vthreads;
+    if (per <= 1) odi_rc = launch_pdl((rmsnorm_add_vec_kernel<1>), dim3(n), dim3(vthreads), 0, stream, (float4*)hidden, (const float4*)y, (const float4*)w, H4, eps);
+    else if (per <= 2) odi_rc = launch_pdl((rmsnorm_add_vec_kernel<2>), dim3(n), dim3(vthreads), 0, stream, (float4*)hidden, (const float4*)y, (const float4*)w, H4, eps);
+    else if (per <= 4) odi_rc = launch_pdl((rmsnorm_add_vec_kernel<4>), dim3(n), dim3(vthreads), 0, stream, (float4*)hidden, (const float4*)y, (const float4*)w, H4, eps);
+    else odi_rc = launch_pdl((rmsnorm_add_vec_kernel<0>), dim3(n), dim3(vthreads), 0, stream, (float4*)hidden, (const float4*)y, (const float4*)w, H4, eps);
+    return launch_status();
+  }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   odi_rc = launch_pdl((rmsnorm_add_kernel), dim3(n), dim3(threads), 0, stream, hidden, y, w, H, eps);
   return launch_status();
@@ -213,11 +314,57 @@ __global__ void gated_row_add_kernel(float* __restrict__ acc, const Y* __restric
   for (int i = threadIdx.x; i < H; i += blockDim.x) acc[t * H + i] = fmaf(gate, to_f<Y>(y[t * H + i]), acc[t * H + i]);
 }
 
+// bf16 x and gate with fp32 or bf16 y, eight lanes at a time (K and H multiples of 8, aligned rows).
+template <typename Y>
+__global__ void gated_row_add_vec_kernel(float* __restrict__ acc, const Y* __restrict__ y, const bf16* __restrict__ x,
+                                         const bf16* __restrict__ g, int H, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const size_t t = blockIdx.x;
+  float dot = 0.f;
+  for (int i = threadIdx.x * 8; i < K; i += blockDim.x * 8) {
+    const uint4 xr = *(const uint4*)(x + t * K + i), gr = *(const uint4*)(g + i);
+    const __nv_bfloat162* xh = (const __nv_bfloat162*)&xr;
+    const __nv_bfloat162* gh = (const __nv_bfloat162*)&gr;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(xh[e]), b = __bfloat1622float2(gh[e]);
+      dot = fmaf(a.x, b.x, dot); dot = fmaf(a.y, b.y, dot);
+    }
+  }
+  dot = block_sum(dot, scratch);
+  const float gate = 1.0f / (1.0f + expf(-dot));
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float v[8];
+    if (sizeof(Y) == 4) {
+      const float4 lo = *(const float4*)((const float*)y + t * H + i), hi = *(const float4*)((const float*)y + t * H + i + 4);
+      v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+    } else {
+      const uint4 raw = *(const uint4*)((const bf16*)y + t * H + i);
+      const __nv_bfloat162* h2 = (const __nv_bfloat162*)&raw;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+    }
+    float4* dst = (float4*)(acc + t * H + i);
+    float4 lo = dst[0], hi = dst[1];
+    lo.x = fmaf(gate, v[0], lo.x); lo.y = fmaf(gate, v[1], lo.y); lo.z = fmaf(gate, v[2], lo.z); lo.w = fmaf(gate, v[3], lo.w);
+    hi.x = fmaf(gate, v[4], hi.x); hi.y = fmaf(gate, v[5], hi.y); hi.z = fmaf(gate, v[6], hi.z); hi.w = fmaf(gate, v[7], hi.w);
+    dst[0] = lo; dst[1] = hi;
+  }
+}
+
 // y_is_t: y has the dtype of x; else it is fp32.
 extern "C" int odi_gated_row_add(float* acc, const void* y, const void* x, const void* g, int n, int H, int K, int y_is_t,
                                  int dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  if (dtype == 1 && H % 8 == 0 && K % 8 == 0 && ((uintptr_t)acc | (uintptr_t)y | (uintptr_t)x | (uintptr_t)g) % 16 == 0) {
+    const int vthreads = H >= 2048 ? 256 : 128;
+    if (y_is_t) odi_rc = launch_pdl((gated_row_add_vec_kernel<bf16>), dim3(n), dim3(vthreads), 0, stream, acc, (const bf16*)y, (const bf16*)x, (const bf16*)g, H, K);
+    else odi_rc = launch_pdl((gated_row_add_vec_kernel<float>), dim3(n), dim3(vthreads), 0, stream, acc, (const float*)y, (const bf16*)x, (const bf16*)g, H, K);
+    return launch_status();
+  }
   if (dtype == 0) odi_rc = launch_pdl((gated_row_add_kernel<float, float>), dim3(n), dim3(threads), 0, stream, acc, (const float*)y, (const float*)x, (const float*)g, H, K);
   else if (y_is_t) odi_rc = launch_pdl((gated_row_add_kernel<bf16, bf16>), dim3(n), dim3(threads), 0, stream, acc, (const bf16*)y, (const bf16*)x, (const bf16*)g, H, K);
   else odi_rc = launch_pdl((gated_row_add_kernel<bf16, float>), dim3(n), dim3(threads), 0, stream, acc, (const float*)y, (const bf16*)x, (const bf16*)g, H, K);

@@ -513,9 +513,50 @@ __global__ void rmsnorm_scaled_kernel(const float* __restrict__ x, const float* 
   for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f<T>(xr[i] * inv * scale[i]);
 }
 
+// The same with four lanes per thread kept in registers between the two passes (H a multiple of 4 and at most
+// 4 * NV * blockDim.x, aligned rows).
+template <typename T, int NV>
+__global__ void rmsnorm_scaled_vec_kernel(const float4* __restrict__ x, const float4* __restrict__ scale,
+                                          T* __restrict__ out, const int* __restrict__ rows, int H4, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const float4* xr = x + (size_t)(rows ? rows[r] : r) * H4;
+  float4 keep[NV];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    keep[j] = i < H4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss += keep[j].x * keep[j].x + keep[j].y * keep[j].y + keep[j].z * keep[j].z + keep[j].w * keep[j].w;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)(4 * H4) + eps);
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < H4) {
+      const float4 g = scale[i];
+      const float4 v = make_float4(keep[j].x * inv * g.x, keep[j].y * inv * g.y, keep[j].z * inv * g.z, keep[j].w * inv * g.w);
+      Pack4<T>::store(out + ((size_t)r * H4 + i) * 4, v.x, v.y, v.z, v.w);
+    }
+  }
+}
+
 extern "C" int odi_rmsnorm_scaled(const float* x, const float* scale, void* out, const int* rows, int n, int H,
                                   float eps, int dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
+  if (H % 4 == 0 && H <= 16384 && ((uintptr_t)x | (uintptr_t)scale | (uintptr_t)out) % 16 == 0) {
+    const int H4 = H / 4;
+    const int vthreads = H4 >= 1024 ? 512 : (H4 >= 256 ? 256 : (H4 >= 128 ? 128 : 64));
+    const int per = (H4 + vthreads - 1) / vthreads;
+#define ODI_RS(T, NV) odi_rc = launch_pdl((rmsnorm_scaled_vec_kernel<T, NV>), dim3(n), dim3(vthreads), 0, stream, (const float4*)x, (const float4*)scale, (T*)out, rows, H4, eps)
+    if (dtype == 0) { if (per <= 1) ODI_RS(float, 1); else if (per <= 2) ODI_RS(float, 2); else if (per <= 4) ODI_RS(float, 4); else ODI_RS(float, 8); }
+    else { if (per <= 1) ODI_RS(bf16, 1); else if (per <= 2) ODI_RS(bf16, 2); else if (per <= 4) ODI_RS(bf16, 4); else ODI_RS(bf16, 8); }
+#undef ODI_RS
+    return launch_status();
+  }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   if (dtype == 0) odi_rc = launch_pdl((rmsnorm_scaled_kernel<float>), dim3(n), dim3(threads), 0, stream, x, scale, (float*)out, rows, H, eps);
   else odi_rc = launch_pdl((rmsnorm_scaled_kernel<bf16>), dim3(n), dim3(threads), 0, stream, x, scale, (bf16*)out, rows, H, eps);

@@ -231,9 +231,50 @@ __global__ void moe_combine_kernel(CombineArgs a) {
   }
 }
 
+// bf16 inputs, eight lanes per thread (H a multiple of 8, aligned rows): the same sums in the same order.
+__global__ void moe_combine_vec_kernel(CombineArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8; i < a.H; i += gridDim.y * blockDim.x * 8) {
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < a.top; ++k) {
+      const int p = t * a.top + k;
+      const int e = a.ids[p];
+      if (e < 0) continue;
+      float v[8];
+      if (e < a.n_experts && !a.out_is_t) {
+        const float* src = (const float*)a.expert_out + (size_t)a.pos[p] * a.H + i;
+        const float4 lo = *(const float4*)src, hi = *(const float4*)(src + 4);
+        v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+      } else {
+        const bf16* src = e >= a.n_experts ? (const bf16*)a.input + (size_t)t * a.H + i
+                                           : (const bf16*)a.expert_out + (size_t)a.pos[p] * a.H + i;
+        const uint4 raw = *(const uint4*)src;
+        const __nv_bfloat162* h2 = (const __nv_bfloat162*)&raw;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h2[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
+      }
+      const float w = a.weights[p];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum[j] = fmaf(w, v[j], sum[j]);
+    }
+    float4* dst = (float4*)(a.residual + (size_t)t * a.H + i);
+    float4 lo = dst[0], hi = dst[1];
+    lo.x += sum[0]; lo.y += sum[1]; lo.z += sum[2]; lo.w += sum[3]; hi.x += sum[4]; hi.y += sum[5]; hi.z += sum[6]; hi.w += sum[7];
+    dst[0] = lo; dst[1] = hi;
+  }
+}
+
 extern "C" int odi_moe_combine(const CombineArgs* args, int dtype, cudaStream_t stream) {
   const CombineArgs a = *args;
   if (a.n_tokens <= 0) return 0;
+  if (dtype == 1 && a.H % 8 == 0 && ((uintptr_t)a.residual | (uintptr_t)a.expert_out | (uintptr_t)a.input) % 16 == 0) {
+    const int vthreads = a.H >= 2048 ? 256 : (a.H >= 1024 ? 128 : 64);
+    const int vpieces = a.n_tokens >= 512 ? 1 : min(8, (a.H / 8 + vthreads - 1) / vthreads);
+    odi_rc = launch_pdl(moe_combine_vec_kernel, dim3(a.n_tokens, vpieces), dim3(vthreads), 0, stream, a);
+    return launch_status();
+  }
   const int threads = a.H >= 1024 ? 256 : 128;
   // few tokens: a row's lanes over several blocks, so that each thread has one short chain of loads
   const int pieces = a.n_tokens >= 512 ? 1 : min(16, (a.H + threads - 1) / threads);
@@ -256,9 +297,27 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict
   for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = src[c];
 }
 
+// The same in pieces of 16 bytes (row_bytes a multiple of 16, aligned rows).
+__global__ void moe_gather_vec_kernel(const uint4* __restrict__ x, const int* __restrict__ perm, const int* __restrict__ offsets,
+                                      uint4* __restrict__ out, int row16, int top, int n_experts) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x;
+  if (i >= offsets[n_experts]) return;
+  const uint4* src = x + (size_t)(perm[i] / top) * row16;
+  uint4* dst = out + (size_t)i * row16;
+  for (int c = threadIdx.x; c < row16; c += blockDim.x) dst[c] = src[c];
+}
+
 extern "C" int odi_moe_gather(const void* x, const int* perm, const int* offsets, void* out, int n_pairs, int H, int top,
                               int n_experts, int dtype, cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
+  const size_t row_bytes = (size_t)H * (dtype == 0 ? 4 : 2);
+  if (row_bytes % 16 == 0 && ((uintptr_t)x | (uintptr_t)out) % 16 == 0) {
+    const int row16 = (int)(row_bytes / 16);
+    odi_rc = launch_pdl(moe_gather_vec_kernel, dim3(n_pairs), dim3(row16 >= 256 ? 256 : 128), 0, stream, (const uint4*)x, perm, offsets, (uint4*)out, row16, top, n_experts);
+    return launch_status();
+  }
   if (dtype == 0) odi_rc = launch_pdl((moe_gather_kernel<float>), dim3(n_pairs), dim3(128), 0, stream, (const float*)x, perm, offsets, (float*)out, H, top, n_experts);
   else odi_rc = launch_pdl((moe_gather_kernel<bf16>), dim3(n_pairs), dim3(128), 0, stream, (const bf16*)x, perm, offsets, (bf16*)out, H, top, n_experts);
   return launch_status();

@@ -1175,6 +1175,62 @@ def rot_unit_prep(qkv, q_out, k_pool, v_pool, cos_t, sin_t, tok_seq, tok_pos, pa
     _check(lib.odi_rot_unit_prep(byref(args), c_int(dtype_code(qkv.dtype)), _stream()), "rot_unit_prep")
 
 
+class _CappedAttnArgs(Structure):
+    _fields_ = [("q", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p), ("out", c_void_p), ("cu_q", c_void_p),
+                ("past", c_void_p), ("page_start", c_void_p), ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int),
+                ("nkv", c_int), ("ring_pages", c_int), ("window", c_int), ("scale", c_float), ("softcap", c_float)]
+
+
+def attention_capped_supported(dtype: torch.dtype, d: int, dv: int) -> bool:
+    """Whether :func:`attention_capped` takes these heads: bfloat16, key and value widths in steps of 16 up to 256."""
+    return dtype == torch.bfloat16 and d % 16 == 0 and dv % 16 == 0 and 16 <= d <= 256 and 16 <= dv <= 256
+
+
+def attention_capped(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int, nq: int,
+                     nkv: int, d: int, dv: int, page_size: int, ring_pages: int, window: int, scale: float,
+                     softcap: float = 0.0) -> None:
+    """bf16 causal GQA on the tensor cores with squashed scores (``softcap`` c > 0: c tanh(score / c)), a window
+    (0: none; the cache may be a ring of pages) and value rows of ``dv`` lanes, for any mixture of sequences."""
+    if not attention_capped_supported(q.dtype, d, dv) or page_size != 64:
+        raise KernelError(f"attention_capped takes bfloat16 heads in steps of 16 up to 256 and pages of 64 (d={d}, dv={dv})")
+    _require(q, "q", torch.bfloat16)
+    _require(out, "out", torch.bfloat16)
+    _require(k_pool, "k_pool", torch.bfloat16)
+    _require(v_pool, "v_pool", torch.bfloat16)
+    n_tokens = q.numel() // (nq * d)
+    if out.numel() != n_tokens * nq * dv or k_pool.shape[-1] != d or v_pool.shape[-1] != dv:
+        raise KernelError("attention_capped sizes disagree")
+    args = _CappedAttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(cu_q), _ptr(past), _ptr(page_start),
+                           _ptr(page_ids), n_seqs, nq, nkv, ring_pages, window, scale, softcap)
+    lib = load_library("attention_capped_mma", {"ODI_HEAD_DIM": d, "ODI_VALUE_DIM": dv})
+    _check(lib.odi_attention_capped(byref(args), c_int(max_q_len), _stream()), "attention_capped")
+
+
+def attention_capped_decode(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, nq: int, nkv: int,
+                            d: int, dv: int, page_size: int, ring_pages: int, window: int, scale: float,
+                            softcap: float = 0.0, splits: int = 1, partial: Optional[torch.Tensor] = None) -> None:
+    """:func:`attention_capped` for steps in which every sequence brings one token: each sequence's visible keys
+    are cut into ``splits`` ranges that blocks of their own take; ``partial`` (fp32, tokens * nq * splits * (dv + 2))
+    holds their results for the combine kernel."""
+    if not attention_capped_supported(q.dtype, d, dv) or page_size != 64:
+        raise KernelError(f"attention_capped takes bfloat16 heads in steps of 16 up to 256 and pages of 64 (d={d}, dv={dv})")
+    _require(q, "q", torch.bfloat16)
+    _require(out, "out", torch.bfloat16)
+    _require(k_pool, "k_pool", torch.bfloat16)
+    _require(v_pool, "v_pool", torch.bfloat16)
+    if q.numel() != n_seqs * nq * d or out.numel() != n_seqs * nq * dv or k_pool.shape[-1] != d or v_pool.shape[-1] != dv:
+        raise KernelError("attention_capped_decode sizes disagree (one token per sequence)")
+    if splits > 1:
+        need = n_seqs * nq * splits * (dv + 2)
+        if partial is None or partial.numel() < need or partial.dtype != torch.float32:
+            raise KernelError(f"splits={splits} needs an fp32 partial buffer of {need} elements")
+    args = _CappedAttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(cu_q), _ptr(past), _ptr(page_start),
+                           _ptr(page_ids), n_seqs, nq, nkv, ring_pages, window, scale, softcap)
+    lib = load_library("attention_capped_mma", {"ODI_HEAD_DIM": d, "ODI_VALUE_DIM": dv})
+    _check(lib.odi_attention_capped_decode(byref(args), _ptr(partial), c_int(splits), _stream()), "attention_capped_decode",
+           2 if splits > 1 else 1)
+
+
 ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1}
 
 

@@ -4,7 +4,9 @@ Steps of ``forward``: one matrix product for the concatenated q, k, v projection
 own); head preparation (``csrc/capped.cu``): rotation of neighbouring-lane pairs, then every q and k head divided
 by its root mean square, q to the query buffer, k and v to the token's row of the paged cache (a ring of pages
 per sequence when the layer has a window); attention over the cache pages with the scores squashed by
-c tanh(score / c) and keys outside the window left out; the output projection.  Rotation, unit norm, scores and
+c tanh(score / c) and keys outside the window left out (bfloat16 with heads in steps of 16:
+``csrc/attention_capped_mma.cu`` on the tensor cores, a form for prompts and portions and a split-key form for
+single tokens; float32 and other head sizes: the CUDA-core kernel ``csrc/attention_simt.cu``); the output projection.  Rotation, unit norm, scores and
 softmax are fp32 in both compute dtypes.  Every constant (scale, cap, window, eps, rotated lanes, frequency
 scaling) is a field of the spec; a field that is None switches its mechanism off.
 """
@@ -89,19 +91,33 @@ class CappedAttention(Part):
         """The attention output [tokens, heads * value_dim]."""
         s = self.spec
         o = torch.empty((ctx.n_tokens, s.num_heads * s.value_dim), dtype=q.dtype, device=q.device)
+        tensor_cores = ops.attention_capped_supported(q.dtype, self.lanes, s.value_dim)
+        common = dict(n_seqs=ctx.n_seqs, nq=s.num_heads, nkv=s.num_kv_heads, d=self.lanes, dv=s.value_dim, page_size=PAGE_SIZE,
+                      ring_pages=view.kv_group.ring_pages, window=s.window or 0, scale=s.scale, softcap=s.softcap or 0.0)
+        if tensor_cores and ctx.max_q_len > 1:
+            # bf16 prompts and portions: the tensor-core form
+            ops.attention_capped(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
+                                 max_q_len=ctx.max_q_len, **common)
+            return o
         splits, partial = 1, None
         if ctx.max_q_len == 1:
-            # single tokens: cut long key ranges so that enough blocks run side by side
+            # single tokens: cut the visible keys so that enough blocks run side by side
             block_rows = s.num_kv_heads * ((s.num_heads // s.num_kv_heads + 15) // 16)
             keys = ctx.max_kv_len if s.window is None else min(ctx.max_kv_len, s.window)
-            splits = max(1, min(32, 296 // max(ctx.n_seqs * block_rows, 1), (keys + 255) // 256))
+            if tensor_cores:
+                tiles = (keys + 63) // 64 + (1 if s.window is not None else 0)      # a window may straddle one tile more
+                splits = max(1, min(32, 296 // max(ctx.n_seqs * block_rows, 1), tiles))
+            else:
+                splits = max(1, min(32, 296 // max(ctx.n_seqs * block_rows, 1), (keys + 255) // 256))
             if splits > 1:
                 partial = torch.empty((ctx.n_tokens * s.num_heads * splits * (s.value_dim + 2),), dtype=torch.float32,
                                       device=q.device)
-        ops.attention_simt(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids, n_seqs=ctx.n_seqs,
-                           max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads, d=self.lanes, dv=s.value_dim,
-                           page_size=PAGE_SIZE, ring_pages=view.kv_group.ring_pages, window=s.window or 0,
-                           scale=s.scale, splits=splits, partial=partial, softcap=s.softcap or 0.0)
+        if tensor_cores and ctx.max_q_len == 1:
+            ops.attention_capped_decode(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
+                                        splits=splits, partial=partial, **common)
+            return o
+        ops.attention_simt(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
+                           max_q_len=ctx.max_q_len, splits=splits, partial=partial, **common)
         return o
 
 

@@ -131,13 +131,56 @@ def test_attention_kernel_caps_scores_and_keeps_the_window(dtype, window, softca
             assert (got - want).abs().max() < (2e-5 if dtype == torch.float32 else 2e-2), (head, splits)
 
 
+@pytest.mark.parametrize("d,dv", [(32, 48), (16, 16), (96, 32), (128, 128)])
+@pytest.mark.parametrize("window,softcap,T,past,ring", [(None, 5.0, 200, 0, 0), (64, None, 200, 0, 0), (65, 3.0, 131, 100, 0),
+                                                        (1, 2.0, 40, 0, 0), (7, 30.0, 1, 190, 0), (100, 8.0, 300, 500, 8),
+                                                        (129, 20.0, 2, 1000, 5), (70, 9.0, 64, 64, 4), (129, 20.0, 1, 1001, 5), (None, 6.0, 1, 333, 0)])
+def test_tensor_core_attention_caps_scores_and_keeps_the_window(d, dv, window, softcap, T, past, ring):
+    """The bfloat16 tensor-core form against the plain scores, mask and softmax: prompts, portions on top of cached
+    keys, pages and rings of pages (a ring holds the window and the portion, older positions are overwritten)."""
+    g = torch.Generator().manual_seed(T + past + d)
+    nq, nkv, scale, total = 4, 2, 1.5 / d ** 0.5, past + T
+    q = torch.randn(T, nq, d, generator=g).bfloat16()
+    k = torch.randn(total, nkv, d, generator=g).bfloat16()
+    v = torch.randn(total, nkv, dv, generator=g).bfloat16()
+    n_pages = ring or -(-total // 64)
+    pools = []
+    for x in (k, v):
+        pool = torch.zeros((n_pages, nkv, 64, x.shape[-1]), dtype=x.dtype)
+        for p in range(max(0, total - n_pages * 64) if ring else 0, total):       # later positions overwrite older ones
+            pool[(p // 64) % n_pages, :, p % 64] = x[p]
+        pools.append(pool.cuda())
+    out = torch.empty((T, nq * dv), dtype=torch.bfloat16, device="cuda")
+    ints = lambda *values: torch.tensor(values, dtype=torch.int32, device="cuda")
+    ops.attention_capped(q.view(T, -1).cuda(), pools[0], pools[1], out, ints(0, T), ints(past), ints(0, n_pages),
+                         torch.arange(n_pages, dtype=torch.int32, device="cuda"), n_seqs=1, max_q_len=T, nq=nq, nkv=nkv, d=d,
+                         dv=dv, page_size=64, ring_pages=ring, window=window or 0, scale=scale, softcap=softcap or 0.0)
+    see = plain.visible(total, window)[past:]
+    want = []
+    for head in range(nq):
+        s = plain.capped_scores(q[:, head].double(), k[:, head // 2].double(), scale, softcap)
+        want.append(torch.softmax(s.masked_fill(~see, float("-inf")), -1) @ v[:, head // 2].double())
+        assert (out.view(T, nq, dv)[:, head].cpu().double() - want[-1]).abs().max() < 2e-2, head
+    if T == 1:
+        # the form for single tokens, whose blocks take a share of the visible keys each (some shares may be empty)
+        for splits in (1, 2, 3, 7):
+            out.zero_()
+            partial = torch.empty(nq * splits * (dv + 2), dtype=torch.float32, device="cuda") if splits > 1 else None
+            ops.attention_capped_decode(q.view(T, -1).cuda(), pools[0], pools[1], out, ints(0, T), ints(past), ints(0, n_pages),
+                                        torch.arange(n_pages, dtype=torch.int32, device="cuda"), n_seqs=1, nq=nq, nkv=nkv, d=d,
+                                        dv=dv, page_size=64, ring_pages=ring, window=window or 0, scale=scale,
+                                        softcap=softcap or 0.0, splits=splits, partial=partial)
+            for head in range(nq):
+                assert (out.view(T, nq, dv)[:, head].cpu().double() - want[head]).abs().max() < 2e-2, (head, splits)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("where", ["prompt", "decoded"])
 def test_one_outstanding_key_shows_both_edges_of_the_window(dtype, where):
     """All keys are alike but one, which matches the query: with the key on the window's last position the output is
     its value, one position further back it is gone.  The same at a page border, and for the newest key."""
     nq = nkv = 1
-    d, dv, window, scale = 8, 4, 70, 4.0
+    d, dv, window, scale = 16, 16, 70, 4.0
     ints = lambda *values: torch.tensor(values, dtype=torch.int32, device="cuda")
     for pos in (69, 127, 128, 200):                       # the query's position
         for back, seen in ((0, True), (window - 1, True), (window, False), (pos, pos < window)):
@@ -155,12 +198,29 @@ def test_one_outstanding_key_shows_both_edges_of_the_window(dtype, where):
             q = q_rows[past:].to(dtype)
             n_pages = -(-total // 64)
             out = torch.empty((T, dv), dtype=dtype, device="cuda")
+            common = dict(n_seqs=1, max_q_len=T, nq=nq, nkv=nkv, d=d, dv=dv, page_size=64, ring_pages=0, window=window,
+                          scale=scale, softcap=50.0)
+            tables = (ints(0, T), ints(past), ints(0, n_pages), torch.arange(n_pages, dtype=torch.int32, device="cuda"))
             ops.attention_simt(q.view(T, -1).cuda(), _paged(k.to(dtype), n_pages).cuda(), _paged(v.to(dtype), n_pages).cuda(), out,
-                               ints(0, T), ints(past), ints(0, n_pages), torch.arange(n_pages, dtype=torch.int32, device="cuda"),
-                               n_seqs=1, max_q_len=T, nq=nq, nkv=nkv, d=d, dv=dv, page_size=64, ring_pages=0, window=window,
-                               scale=scale, softcap=50.0)
+                               *tables, **common)
             weight = float(out[-1, 1])
             assert (weight > 0.99) if seen else (weight == 0.0), (pos, back, weight)
+            if dtype == torch.bfloat16:                      # the tensor-core form
+                out.zero_()
+                ops.attention_capped(q.view(T, -1).cuda(), _paged(k.to(dtype), n_pages).cuda(), _paged(v.to(dtype), n_pages).cuda(),
+                                     out, *tables, **common)
+                weight = float(out[-1, 1])
+                assert (weight > 0.99) if seen else (weight == 0.0), (pos, back, weight)
+                if T == 1:
+                    for splits in (1, 2):
+                        out.zero_()
+                        partial = torch.empty(splits * (dv + 2), dtype=torch.float32, device="cuda")
+                        decode = {key: value for key, value in common.items() if key != "max_q_len"}
+                        ops.attention_capped_decode(q.view(T, -1).cuda(), _paged(k.to(dtype), n_pages).cuda(),
+                                                    _paged(v.to(dtype), n_pages).cuda(), out, *tables, splits=splits,
+                                                    partial=partial, **decode)
+                        weight = float(out[-1, 1])
+                        assert (weight > 0.99) if seen else (weight == 0.0), (pos, back, weight, splits)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
