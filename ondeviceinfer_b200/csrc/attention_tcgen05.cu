@@ -39,7 +39,8 @@
 // tensor-memory owner, 2..5 = softmax and output of the first head, 6..9 = of the second.
 //
 // Works for any q_len >= 1 on top of any cached length (query t of the step sits at position
-// past + t).  No window.  Compile with -DODI_HEAD_DIM=64 or 128.
+// past + t).  Optional: a window (the walk starts at the tile of the oldest key the CTA's rows see; the page list
+// may be a ring), and scores squashed by c tanh(score / c).  Compile with -DODI_HEAD_DIM=64 or 128.
 //
 // Every wait on an mbarrier is bounded (about two seconds of SM clock): a role that gives up
 // records a code in `status`, raises the CTA's abort flag, and all roles fall through to the
@@ -85,6 +86,9 @@ struct TcAttnArgs {
   int* status;
   int n_seqs, nq, nkv;
   float scale;
+  int window;             // > 0: the query at position p sees keys p - window + 1 .. p only
+  int ring_pages;         // > 0: a sequence's page list is a ring: the page of position p is entry (p / 64) % ring_pages
+  float softcap;          // c > 0: a score (times scale) becomes c tanh(score / c) before the softmax
 };
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -255,18 +259,25 @@ __device__ __forceinline__ void umma_a_tmem(uint32_t d_tmem, uint32_t a_tmem, ui
 // pairs, 32 columns at p_addr) against the row's running maximum; n counts this head's PV products
 // (the one that will read this P is product n), kbase is the first key's position.  Returns false if a
 // wait gave up.  The caller signals P afterwards.
+// `oldest` is the first key the row still sees (0 without a window).  With a cap (two_over_cap > 0) the score
+// times `scale` is squashed first, as c (1 - 2 / (e^(2 x / c) + 1)) = c tanh(x / c), and sl2 is log2(e) alone.
 struct RowState { float m_used, l; };
 __device__ __forceinline__ bool softmax_keys64(uint32_t s_addr, uint32_t p_addr, uint32_t o_addr, int kbase, int pos, float sl2,
-                                               int n, uint32_t pv_done, RowState& st, volatile int* abort_ptr) {
+                                               int n, uint32_t pv_done, RowState& st, volatile int* abort_ptr,
+                                               int oldest = 0, float scale = 1.f, float cap = 0.f, float two_over_cap = 0.f) {
   float s[BNK];
   tmem_ld64(s_addr, s);
+  if (cap > 0.f) {
+#pragma unroll
+    for (int i = 0; i < BNK; ++i) s[i] = cap * (1.f - __fdividef(2.f, __expf(s[i] * scale * two_over_cap) + 1.f));
+  }
   float mx = -INFINITY;
-  if (kbase + BNK - 1 <= pos) {
+  if (kbase + BNK - 1 <= pos && kbase >= oldest) {
 #pragma unroll
     for (int i = 0; i < BNK; ++i) mx = fmaxf(mx, s[i]);
   } else {
 #pragma unroll
-    for (int i = 0; i < BNK; ++i) { if (kbase + i > pos) s[i] = -INFINITY; mx = fmaxf(mx, s[i]); }
+    for (int i = 0; i < BNK; ++i) { if (kbase + i > pos || kbase + i < oldest) s[i] = -INFINITY; mx = fmaxf(mx, s[i]); }
   }
   // Raise the maximum this row's P is taken against only when it is exceeded by a wide margin;
   // what O holds for the row was taken against the old one and is scaled down first.  The
@@ -291,10 +302,13 @@ __device__ __forceinline__ bool softmax_keys64(uint32_t s_addr, uint32_t p_addr,
   if (need) { st.l *= alpha; st.m_used = m_tile; }
   uint32_t packed[BNK / 2];                      // masked scores are -inf: exp2 gives 0
   float sum = 0.f;
+  // a row that has seen no key yet (only under a window: its first tiles may lie before its oldest key) has
+  // nothing but masked scores here; subtracting its maximum of -inf would give NaN instead of 0
+  const float m_sub = st.m_used == -INFINITY ? 0.f : st.m_used;
 #pragma unroll
   for (int i = 0; i < BNK / 2; ++i) {
-    const float p0 = fast_exp2(fmaf(s[2 * i], sl2, -st.m_used));
-    const float p1 = fast_exp2(fmaf(s[2 * i + 1], sl2, -st.m_used));
+    const float p0 = fast_exp2(fmaf(s[2 * i], sl2, -m_sub));
+    const float p1 = fast_exp2(fmaf(s[2 * i + 1], sl2, -m_sub));
     sum += p0 + p1;
     __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
     packed[i] = *(uint32_t*)&pr;
@@ -351,7 +365,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   if (t0 >= q_len) return;                       // whole CTA: nothing allocated yet
   const int past = a.past[seq];
   const int nt = min(BM, q_len - t0);
-  const int n_tiles = (past + t0 + nt + BNK - 1) / BNK;
+  // key tiles from the one that holds the oldest key any row of the CTA sees up to the diagonal
+  const int tile_lo = a.window > 0 ? max(0, past + t0 - a.window + 1) / BNK : 0;
+  const int n_tiles = (past + t0 + nt + BNK - 1) / BNK - tile_lo;
   const int* pages = a.page_ids + a.page_start[seq];
 
   const uint32_t bar0 = smem_u32(&bars[0]);
@@ -391,7 +407,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       auto load_page = [&](int j, const CUtensorMap* map, uint8_t* ring, uint32_t full, uint32_t empty) {
         const int s = j % RING;
         if (!mbar_wait(empty + 8 * s, ((uint32_t)(j / RING) & 1u) ^ 1u, abort_ptr)) { ok = false; return; }
-        const int row = (pages[j] * a.nkv + hk) * BNK;
+        const int entry = a.ring_pages > 0 ? (tile_lo + j) % a.ring_pages : tile_lo + j;
+        const int row = (pages[entry] * a.nkv + hk) * BNK;
         mbar_expect_tx(full + 8 * s, KV_BYTES);
         for (int kb = 0; kb < KB; ++kb)
           tma_load_2d(smem_u32(ring + (size_t)s * KV_BYTES + kb * BNK * 128), map, kb * 64, row, full + 8 * s);
@@ -460,7 +477,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int row = lane_group * 32 + lane;          // query row inside the tile
     const int pos = past + t0 + row;
     const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
-    const float sl2 = a.scale * LOG2E;
+    const float sl2 = a.softcap > 0.f ? LOG2E : a.scale * LOG2E;
+    const float two_over_cap = a.softcap > 0.f ? 2.f / a.softcap : 0.f;
+    const int oldest = a.window > 0 ? pos - a.window + 1 : 0;
     RowState st = {-INFINITY, 0.f};
     bool ok = true;
     const uint32_t my_p_full = p_full + 16 * tile, my_pv_done = pv_done + 8 * tile;
@@ -472,7 +491,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       tc_fence_after();
       const uint32_t s_addr = tmem_base + lane_addr + S_COL(tile, b);
       // P_j goes over the first 32 columns of this row's scores
-      if (!softmax_keys64(s_addr, s_addr, o_addr, j * BNK, pos, sl2, j, my_pv_done, st, abort_ptr)) { ok = false; break; }
+      if (!softmax_keys64(s_addr, s_addr, o_addr, (tile_lo + j) * BNK, pos, sl2, j, my_pv_done, st, abort_ptr, oldest, a.scale,
+                          a.softcap, two_over_cap)) { ok = false; break; }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(my_p_full + 8 * b);

@@ -6,7 +6,9 @@ by its root mean square, q to the query buffer, k and v to the token's row of th
 per sequence when the layer has a window); attention over the cache pages with the scores squashed by
 c tanh(score / c) and keys outside the window left out (bfloat16 with heads in steps of 16:
 ``csrc/attention_capped_mma.cu`` on the tensor cores, a form for prompts and portions and a split-key form for
-single tokens; float32 and other head sizes: the CUDA-core kernel ``csrc/attention_simt.cu``); the output projection.  Rotation, unit norm, scores and
+single tokens; prompts with key and value heads of 64 or 128 lanes: ``csrc/attention_tcgen05.cu``, the kernel of
+the plain attention, which takes the window, the ring and the cap as arguments; float32 and other head sizes: the
+CUDA-core kernel ``csrc/attention_simt.cu``); the output projection.  Rotation, unit norm, scores and
 softmax are fp32 in both compute dtypes.  Every constant (scale, cap, window, eps, rotated lanes, frequency
 scaling) is a field of the spec; a field that is None switches its mechanism off.
 """
@@ -20,6 +22,7 @@ from ..config.specs import CappedAttentionSpec
 from ..kernels import ops
 from ..weights.tensors import TensorDecl
 from .base import Part, build_part, register_part
+from .attention import TCGEN05_MIN_Q_LEN
 from .linear import linear
 
 
@@ -94,8 +97,16 @@ class CappedAttention(Part):
         tensor_cores = ops.attention_capped_supported(q.dtype, self.lanes, s.value_dim)
         common = dict(n_seqs=ctx.n_seqs, nq=s.num_heads, nkv=s.num_kv_heads, d=self.lanes, dv=s.value_dim, page_size=PAGE_SIZE,
                       ring_pages=view.kv_group.ring_pages, window=s.window or 0, scale=s.scale, softcap=s.softcap or 0.0)
+        if (tensor_cores and ctx.max_q_len > TCGEN05_MIN_Q_LEN and self.lanes == s.value_dim
+                and self.lanes in ops.TCGEN05_ATTENTION_HEAD_DIMS):
+            # bf16 prompts with heads of 64 or 128 lanes: scores and outputs in tensor memory (tcgen05)
+            ops.attention_tcgen05(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids, n_seqs=ctx.n_seqs,
+                                  max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads, d=self.lanes, page_size=PAGE_SIZE,
+                                  scale=s.scale, window=s.window or 0, ring_pages=view.kv_group.ring_pages,
+                                  softcap=s.softcap or 0.0)
+            return o
         if tensor_cores and ctx.max_q_len > 1:
-            # bf16 prompts and portions: the tensor-core form
+            # other bf16 prompts and portions: the mma.sync form
             ops.attention_capped(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
                                  max_q_len=ctx.max_q_len, **common)
             return o

@@ -131,7 +131,7 @@ def test_attention_kernel_caps_scores_and_keeps_the_window(dtype, window, softca
             assert (got - want).abs().max() < (2e-5 if dtype == torch.float32 else 2e-2), (head, splits)
 
 
-@pytest.mark.parametrize("d,dv", [(32, 48), (16, 16), (96, 32), (128, 128)])
+@pytest.mark.parametrize("d,dv", [(32, 48), (16, 16), (96, 32), (128, 128), (64, 64)])
 @pytest.mark.parametrize("window,softcap,T,past,ring", [(None, 5.0, 200, 0, 0), (64, None, 200, 0, 0), (65, 3.0, 131, 100, 0),
                                                         (1, 2.0, 40, 0, 0), (7, 30.0, 1, 190, 0), (100, 8.0, 300, 500, 8),
                                                         (129, 20.0, 2, 1000, 5), (70, 9.0, 64, 64, 4), (129, 20.0, 1, 1001, 5), (None, 6.0, 1, 333, 0)])
@@ -161,6 +161,16 @@ def test_tensor_core_attention_caps_scores_and_keeps_the_window(d, dv, window, s
         s = plain.capped_scores(q[:, head].double(), k[:, head // 2].double(), scale, softcap)
         want.append(torch.softmax(s.masked_fill(~see, float("-inf")), -1) @ v[:, head // 2].double())
         assert (out.view(T, nq, dv)[:, head].cpu().double() - want[-1]).abs().max() < 2e-2, head
+    if d == dv and d in ops.TCGEN05_ATTENTION_HEAD_DIMS and T > 16:
+        # the kernel that keeps scores and outputs in tensor memory takes the same window, ring and cap
+        out.zero_()
+        ops.attention_tcgen05(q.view(T, -1).cuda(), pools[0], pools[1], out, ints(0, T), ints(past), ints(0, n_pages),
+                              torch.arange(n_pages, dtype=torch.int32, device="cuda"), n_seqs=1, max_q_len=T, nq=nq, nkv=nkv, d=d,
+                              page_size=64, scale=scale, window=window or 0, ring_pages=ring, softcap=softcap or 0.0)
+        torch.cuda.synchronize()
+        ops.raise_on_kernel_fault()
+        for head in range(nq):
+            assert (out.view(T, nq, dv)[:, head].cpu().double() - want[head]).abs().max() < 2e-2, ("tcgen05", head)
     if T == 1:
         # the form for single tokens, whose blocks take a share of the visible keys each (some shares may be empty)
         for splits in (1, 2, 3, 7):
