@@ -9,6 +9,7 @@
 //  * concat_cast: out[t] = [a[t] ; b[t]] of two fp32 streams in the compute dtype;
 //  * rmsnorm_add: h[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w, all fp32 (the norm after a sublayer and the
 //    residual add in one pass);
+//  * rmsnorm_add_norm: the same followed by the norm that the next sublayer takes of the sum, the row kept in registers;
 //  * gated_row_add: acc[t] += sigmoid(x[t] . g) * y[t] (an expert that every token takes, scaled by a number per token).
 #include "common.cuh"
 
@@ -296,6 +297,74 @@ extern "C" int odi_rmsnorm_add(float* hidden, const float* y, const float* w, in
   }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   odi_rc = launch_pdl((rmsnorm_add_kernel), dim3(n), dim3(threads), 0, stream, hidden, y, w, H, eps);
+  return launch_status();
+}
+
+// rmsnorm_add and the norm that the next sublayer takes of the sum, in one pass: the row of the sum stays in
+// registers (NV float4 per thread).  h += y * rsqrt(mean(y^2) + eps) * w; out = T(h * rsqrt(mean(h^2) + eps2) * w2).
+template <typename T, int NV>
+__global__ void rmsnorm_add_norm_kernel(float4* __restrict__ hidden, const float4* __restrict__ y, const float4* __restrict__ w,
+                                        float eps, const float4* __restrict__ w2, float eps2, T* __restrict__ out, int H4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const size_t base = (size_t)blockIdx.x * H4;
+  float4 keep[NV];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    keep[j] = i < H4 ? y[base + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss += keep[j].x * keep[j].x + keep[j].y * keep[j].y + keep[j].z * keep[j].z + keep[j].w * keep[j].w;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)(4 * H4) + eps);
+  float ss2 = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < H4) {
+      float4 h = hidden[base + i];
+      const float4 g = w[i];
+      h.x += keep[j].x * inv * g.x; h.y += keep[j].y * inv * g.y; h.z += keep[j].z * inv * g.z; h.w += keep[j].w * inv * g.w;
+      hidden[base + i] = h;
+      keep[j] = h;
+      ss2 += h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
+    }
+  }
+  ss2 = block_sum(ss2, scratch);
+  const float inv2 = 1.0f / sqrtf(ss2 / (float)(4 * H4) + eps2);
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < H4) {
+      const float4 g = w2[i];
+      const float4 v = make_float4(keep[j].x * inv2 * g.x, keep[j].y * inv2 * g.y, keep[j].z * inv2 * g.z, keep[j].w * inv2 * g.w);
+      if (sizeof(T) == 4) {
+        ((float4*)out)[base + i] = v;
+      } else {
+        uint2 packed;
+        *(__nv_bfloat162*)&packed.x = __floats2bfloat162_rn(v.x, v.y);
+        *(__nv_bfloat162*)&packed.y = __floats2bfloat162_rn(v.z, v.w);
+        ((uint2*)out)[base + i] = packed;
+      }
+    }
+  }
+}
+
+extern "C" int odi_rmsnorm_add_norm(float* hidden, const float* y, const float* w, float eps, const float* w2, float eps2,
+                                    void* out, int n, int H, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (H % 4 != 0 || H > 8192 || ((uintptr_t)hidden | (uintptr_t)y | (uintptr_t)w | (uintptr_t)w2 | (uintptr_t)out) % 16 != 0)
+    return ODI_ERR_UNSUPPORTED;
+  const int H4 = H / 4;
+  const int threads = H4 >= 1024 ? 512 : (H4 >= 256 ? 256 : (H4 >= 128 ? 128 : 64));
+  const int per = (H4 + threads - 1) / threads;
+#define ODI_RAN(T, NV) odi_rc = launch_pdl((rmsnorm_add_norm_kernel<T, NV>), dim3(n), dim3(threads), 0, stream, (float4*)hidden, \
+    (const float4*)y, (const float4*)w, eps, (const float4*)w2, eps2, (T*)out, H4)
+  if (dtype == 0) { if (per <= 1) ODI_RAN(float, 1); else if (per <= 2) ODI_RAN(float, 2); else ODI_RAN(float, 4); }
+  else { if (per <= 1) ODI_RAN(bf16, 1); else if (per <= 2) ODI_RAN(bf16, 2); else ODI_RAN(bf16, 4); }
+#undef ODI_RAN
   return launch_status();
 }
 

@@ -50,6 +50,7 @@
 #define EPI_RESIDUAL 2
 #define EPI_SWIGLU 3
 #define EPI_HEAD_PREP 4    // the rows of w are q, k and v heads of 128: per-head norm, rotation, cache write
+#define EPI_GELU 5         // bf16 out = gelu(acc), the exact (erf) form
 
 #define BM 128             // token rows per CTA (the lanes of its tensor memory); a tile has 2 * BM
 #define BN 256             // accumulator columns per tile
@@ -148,6 +149,7 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
+__device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f)); }
 
 // ------------------------------------------------------------------------------ the kernel
 
@@ -468,8 +470,8 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 const int e = 8 * q + 2 * i;
-                const float lo = GATE ? silu_f(v[e]) * u[e] : v[e];
-                const float hi = GATE ? silu_f(v[e + 1]) * u[e + 1] : v[e + 1];
+                const float lo = GATE ? silu_f(v[e]) * u[e] : (EPI == EPI_GELU ? gelu_erf_f(v[e]) : v[e]);
+                const float hi = GATE ? silu_f(v[e + 1]) * u[e + 1] : (EPI == EPI_GELU ? gelu_erf_f(v[e + 1]) : v[e + 1]);
                 __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
                 w[i] = *(uint32_t*)&pr;
               }
@@ -651,6 +653,7 @@ extern "C" int odi_gemm_prefill_bf16(const void* x, const void* w, void* out, in
   }
   switch (epi) {
     case EPI_STORE_BF16: return launch<EPI_STORE_BF16>(mx, mw, mo, a, sms, stream);
+    case EPI_GELU: return launch<EPI_GELU>(mx, mw, mo, a, sms, stream);
     case EPI_STORE_F32: return launch<EPI_STORE_F32>(mx, mw, mo, a, sms, stream);
     case EPI_RESIDUAL: return launch<EPI_RESIDUAL>(mx, mw, mo, a, sms, stream);
     case EPI_SWIGLU: return launch<EPI_SWIGLU>(mx, mw, mo, a, sms, stream);

@@ -35,6 +35,7 @@
 #define EPI_RESIDUAL 2     // out_f32[token, n] += acc
 #define EPI_SWIGLU 3       // out_bf16[token, n] = silu(acc_gate) * acc_up   (DUAL)
 #define EPI_HEAD_PREP 4    // the rows are q, k and v heads of 128: per-head norm, rotation, cache write
+#define EPI_GELU 5         // out_bf16[token, n] = gelu(acc), the exact (erf) form
 
 #define BM 128             // features per tile (UMMA M)
 #define BK 64              // k per stage: 64 bf16 = one 128-byte swizzle row
@@ -270,6 +271,7 @@ __device__ __forceinline__ float emit(const GemmArgs& a, int token, int n, float
   else if (EPI == EPI_STORE_F32) ((float*)a.out)[at] = v;
   else if (EPI == EPI_RESIDUAL) { const float r = ((float*)a.out)[at] + v; ((float*)a.out)[at] = r; return r; }
   else if (EPI == EPI_SWIGLU) ((bf16*)a.out)[at] = __float2bfloat16_rn(silu_f(v) * v2);
+  else if (EPI == EPI_GELU) ((bf16*)a.out)[at] = __float2bfloat16_rn(0.5f * v * (1.0f + erff(v * 0.70710678118654752440f)));
   return 0.f;
 }
 
@@ -891,6 +893,7 @@ static int dispatch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& mx, c
   }
   switch (epi) {
     case EPI_STORE_BF16: return launch<BN, false, EPI_STORE_BF16, CLUSTER>(mw, mx, a, grid, stream);
+    case EPI_GELU: return launch<BN, false, EPI_GELU, CLUSTER>(mw, mx, a, grid, stream);
     case EPI_STORE_F32: return launch<BN, false, EPI_STORE_F32, CLUSTER>(mw, mx, a, grid, stream);
     case EPI_RESIDUAL: return launch<BN, false, EPI_RESIDUAL, CLUSTER>(mw, mx, a, grid, stream);
     case EPI_SWIGLU:

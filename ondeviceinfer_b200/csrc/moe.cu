@@ -8,7 +8,8 @@
 //  table    routing without a router: a token's choices are row `token id` of an integer table, each with the
 //           same weight (out-of-range entries take no place).
 //  count    per (token, choice) pair whose output is a real expert: its rank among the pairs of that expert.
-//  plan     one block: the experts' offsets in the sorted order of pairs and the table of row tiles.
+//  plan     one warp: the experts' offsets in the sorted order of pairs and the table of row tiles.
+//           (A step of few pairs does count, plan and scatter in one block and one launch.)
 //  scatter  per pair: its place in the sorted order (`pos`) and the order itself (`perm`).
 //  combine  per token: residual += sum over its choices, in the order of the choices, of weight times the
 //           expert's output row -- or times the token's own input for an identity output (index >= n_experts).
@@ -157,23 +158,106 @@ __global__ void moe_count_kernel(GroupingArgs a) {
   if (e >= 0 && e < a.n_experts) a.rank[p] = atomicAdd(&a.counts[e], 1);
 }
 
+// One warp: experts 32 at a time, their offsets and tile counts by prefix sums over the lanes, every lane then
+// writes the tiles of its own expert.
 __global__ void moe_plan_kernel(GroupingArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  if (threadIdx.x != 0) return;
-  int off = 0, tiles = 0;
-  for (int e = 0; e < a.n_experts; ++e) {
-    const int c = a.counts[e];
-    a.counts[e] = 0;
-    a.offsets[e] = off;
-    for (int r = 0; r < c && tiles < a.max_tiles; r += a.tm) {
-      a.tile_group[tiles] = e; a.tile_row0[tiles] = off + r; a.tile_rows[tiles] = min(a.tm, c - r);
-      ++tiles;
+  const int lane = threadIdx.x;
+  int off = 0, tiles = 0;                       // running totals, the same in every lane
+  for (int e0 = 0; e0 < a.n_experts; e0 += 32) {
+    const int e = e0 + lane;
+    const int c = e < a.n_experts ? a.counts[e] : 0;
+    if (e < a.n_experts) a.counts[e] = 0;
+    const int t = (c + a.tm - 1) / a.tm;
+    int c_in = c, t_in = t;                     // inclusive prefix sums
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int cu = __shfl_up_sync(0xffffffffu, c_in, o), tu = __shfl_up_sync(0xffffffffu, t_in, o);
+      if (lane >= o) { c_in += cu; t_in += tu; }
     }
-    off += c;
+    const int my_off = off + c_in - c;
+    int my_tile = tiles + t_in - t;
+    if (e < a.n_experts) {
+      a.offsets[e] = my_off;
+      for (int r = 0; r < c && my_tile < a.max_tiles; r += a.tm, ++my_tile) {
+        a.tile_group[my_tile] = e; a.tile_row0[my_tile] = my_off + r; a.tile_rows[my_tile] = min(a.tm, c - r);
+      }
+    }
+    off += __shfl_sync(0xffffffffu, c_in, 31);
+    tiles += __shfl_sync(0xffffffffu, t_in, 31);
   }
-  a.offsets[a.n_experts] = off;
-  a.n_tiles[0] = tiles;
+  if (lane == 0) {
+    a.offsets[a.n_experts] = off;
+    a.n_tiles[0] = min(tiles, a.max_tiles);
+  }
+}
+
+// Few pairs (single-token steps): count, plan and scatter by one block in one launch, the counts in shared memory
+// (the global `counts` stay zero).  Up to SMALL_PAIRS pairs; shared memory holds 2 * n_experts + 1 ints.
+#define SMALL_PAIRS 2048
+__global__ void __launch_bounds__(256)
+moe_group_small_kernel(GroupingArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ int sh[];
+  int* cnt = sh;
+  int* offs = sh + a.n_experts;
+  const int tid = threadIdx.x;
+  for (int e = tid; e < a.n_experts; e += 256) cnt[e] = 0;
+  __syncthreads();
+  int my_e[SMALL_PAIRS / 256], my_rank[SMALL_PAIRS / 256];
+#pragma unroll
+  for (int j = 0; j < SMALL_PAIRS / 256; ++j) {
+    const int p = tid + j * 256;
+    my_e[j] = -1;
+    if (p < a.n_pairs) {
+      const int e = a.ids[p];
+      if (e >= 0 && e < a.n_experts) { my_e[j] = e; my_rank[j] = atomicAdd(&cnt[e], 1); }
+    }
+  }
+  __syncthreads();
+  if (tid < 32) {
+    // the same walk as moe_plan_kernel, over the counts in shared memory
+    int off = 0, tiles = 0;
+    for (int e0 = 0; e0 < a.n_experts; e0 += 32) {
+      const int e = e0 + tid;
+      const int c = e < a.n_experts ? cnt[e] : 0;
+      const int t = (c + a.tm - 1) / a.tm;
+      int c_in = c, t_in = t;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int cu = __shfl_up_sync(0xffffffffu, c_in, o), tu = __shfl_up_sync(0xffffffffu, t_in, o);
+        if (tid >= o) { c_in += cu; t_in += tu; }
+      }
+      const int my_off = off + c_in - c;
+      int my_tile = tiles + t_in - t;
+      if (e < a.n_experts) {
+        offs[e] = my_off;
+        a.offsets[e] = my_off;
+        for (int r = 0; r < c && my_tile < a.max_tiles; r += a.tm, ++my_tile) {
+          a.tile_group[my_tile] = e; a.tile_row0[my_tile] = my_off + r; a.tile_rows[my_tile] = min(a.tm, c - r);
+        }
+      }
+      off += __shfl_sync(0xffffffffu, c_in, 31);
+      tiles += __shfl_sync(0xffffffffu, t_in, 31);
+    }
+    if (tid == 0) {
+      a.offsets[a.n_experts] = off;
+      a.n_tiles[0] = min(tiles, a.max_tiles);
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < SMALL_PAIRS / 256; ++j) {
+    const int p = tid + j * 256;
+    if (my_e[j] >= 0) {
+      const int place = offs[my_e[j]] + my_rank[j];
+      a.rank[p] = my_rank[j];
+      a.pos[p] = place;
+      a.perm[place] = p;
+    }
+  }
 }
 
 __global__ void moe_scatter_kernel(GroupingArgs a) {
@@ -193,6 +277,10 @@ extern "C" int odi_moe_group(const GroupingArgs* args, cudaStream_t stream) {
   const GroupingArgs a = *args;
   if (a.n_pairs <= 0) return 0;
   if (a.n_experts <= 0 || a.tm <= 0 || a.max_tiles < (a.n_pairs + a.tm - 1) / a.tm + a.n_experts) return ODI_ERR_ARGUMENT;
+  if (a.n_pairs <= SMALL_PAIRS && a.n_experts <= 4096) {
+    odi_rc = launch_pdl(moe_group_small_kernel, dim3(1), dim3(256), sizeof(int) * (2 * (size_t)a.n_experts + 1), stream, a);
+    return launch_status();
+  }
   const int blocks = (a.n_pairs + 255) / 256;
   odi_rc = launch_pdl(moe_count_kernel, dim3(blocks), dim3(256), 0, stream, a);
   if (odi_rc == 0) odi_rc = launch_pdl(moe_plan_kernel, dim3(1), dim3(32), 0, stream, a);
@@ -208,6 +296,7 @@ struct CombineArgs {
   const float* weights;
   const int* pos;
   int n_tokens, H, top, n_experts, out_is_t;
+  int assign;             // the sums replace the rows of `residual` instead of being added to them
 };
 
 template <typename T>
@@ -227,7 +316,8 @@ __global__ void moe_combine_kernel(CombineArgs a) {
       else v = ((const float*)a.expert_out)[(size_t)a.pos[p] * a.H + i];
       sum = fmaf(a.weights[p], v, sum);
     }
-    a.residual[(size_t)t * a.H + i] += sum;
+    if (a.assign) a.residual[(size_t)t * a.H + i] = sum;
+    else a.residual[(size_t)t * a.H + i] += sum;
   }
 }
 
@@ -260,7 +350,8 @@ __global__ void moe_combine_vec_kernel(CombineArgs a) {
       for (int j = 0; j < 8; ++j) sum[j] = fmaf(w, v[j], sum[j]);
     }
     float4* dst = (float4*)(a.residual + (size_t)t * a.H + i);
-    float4 lo = dst[0], hi = dst[1];
+    float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+    if (!a.assign) { lo = dst[0]; hi = dst[1]; }
     lo.x += sum[0]; lo.y += sum[1]; lo.z += sum[2]; lo.w += sum[3]; hi.x += sum[4]; hi.y += sum[5]; hi.z += sum[6]; hi.w += sum[7];
     dst[0] = lo; dst[1] = hi;
   }

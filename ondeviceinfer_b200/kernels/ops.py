@@ -257,7 +257,7 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Opti
                             c_int(K), c_int(K), c_int(N), c_int(N), _stream()), "gemm_f32")
 
 
-EPI_STORE_BF16, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU, EPI_HEAD_PREP = 0, 1, 2, 3, 4
+EPI_STORE_BF16, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU, EPI_HEAD_PREP, EPI_GELU = 0, 1, 2, 3, 4, 5
 
 _gemm_state = {}
 
@@ -391,7 +391,8 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
     """Tensor-core product out = epilogue(x w^T): x [tokens, K] bf16, w [rows, K] bf16.
 
     ``EPI_STORE_BF16`` / ``EPI_STORE_F32``: out [tokens, rows]; ``EPI_RESIDUAL``: out (fp32) += product;
-    ``EPI_SWIGLU``: w holds the gate rows then the up rows, out [tokens, rows / 2] = silu(gate) * up.
+    ``EPI_SWIGLU``: w holds the gate rows then the up rows, out [tokens, rows / 2] = silu(gate) * up;
+    ``EPI_GELU``: out [tokens, rows] = gelu(product) in bf16 (the exact erf form).
     ``cluster``: let 2..8 K splits exchange their partials inside a thread-block cluster (else, and for
     more splits, through global scratch and a ticket).
     ``norm = (rows, weight, parts, eps)`` instead of ``x``: the operand is RMSNorm(rows) * weight with the
@@ -449,7 +450,7 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
         if w.shape[1] != K:
             raise KernelError(f"gemm sizes disagree: x {tuple(x_like.shape)}, w {tuple(w.shape)}")
     else:
-        _require(out, "out", torch.bfloat16 if epi in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32, 2)
+        _require(out, "out", torch.bfloat16 if epi in (EPI_STORE_BF16, EPI_SWIGLU, EPI_GELU) else torch.float32, 2)
         if w.shape[1] != K or out.shape != (tokens, n_out) or (epi == EPI_SWIGLU and w_rows % 2):
             raise KernelError(f"gemm sizes disagree: x {tuple(x_like.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     if sumsq_out is not None:
@@ -539,9 +540,9 @@ def gemm_prefill_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tens
         if not gemm_bf16_supported(x, w):
             raise KernelError(f"gemm_prefill_tcgen05 needs K a multiple of 8 and 16-byte aligned operands (K={K})")
     else:
-        if epi not in (EPI_STORE_BF16, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU):
+        if epi not in (EPI_STORE_BF16, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU, EPI_GELU):
             raise KernelError(f"gemm_prefill_bf16 has no epilogue {epi}")
-        _require(out, "out", torch.bfloat16 if epi in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32, 2)
+        _require(out, "out", torch.bfloat16 if epi in (EPI_STORE_BF16, EPI_SWIGLU, EPI_GELU) else torch.float32, 2)
         if w.shape[1] != K or out.shape != (tokens, n_out) or (epi == EPI_SWIGLU and w_rows % 2):
             raise KernelError(f"gemm sizes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
         if not gemm_prefill_supported(x, w, n_out, out.dtype):
@@ -1080,7 +1081,7 @@ def moe_group(ids: torch.Tensor, counts: torch.Tensor, table: RoutingTable) -> N
                          _ptr(table.perm), _ptr(table.tile_group), _ptr(table.tile_row0), _ptr(table.tile_rows),
                          _ptr(table.n_tiles), table.n_pairs, table.n_experts, table.tm, table.max_tiles)
     lib = load_library("moe")
-    _check(lib.odi_moe_group(byref(args), _stream()), "moe_group", 3)
+    _check(lib.odi_moe_group(byref(args), _stream()), "moe_group", 1 if table.n_pairs <= 2048 and table.n_experts <= 4096 else 3)
 
 
 def moe_gather(x: torch.Tensor, table: RoutingTable, out: torch.Tensor) -> None:
@@ -1098,13 +1099,13 @@ def moe_gather(x: torch.Tensor, table: RoutingTable, out: torch.Tensor) -> None:
 class _CombineArgs(Structure):
     _fields_ = [("residual", c_void_p), ("expert_out", c_void_p), ("input", c_void_p), ("ids", c_void_p),
                 ("weights", c_void_p), ("pos", c_void_p), ("n_tokens", c_int), ("H", c_int), ("top", c_int),
-                ("n_experts", c_int), ("out_is_t", c_int)]
+                ("n_experts", c_int), ("out_is_t", c_int), ("assign", c_int)]
 
 
 def moe_combine(residual: torch.Tensor, expert_out: torch.Tensor, x: torch.Tensor, ids: torch.Tensor,
-                weights: torch.Tensor, table: RoutingTable) -> None:
+                weights: torch.Tensor, table: RoutingTable, assign: bool = False) -> None:
     """residual[t] += sum_k weights[t, k] * (row pos[t, k] of ``expert_out``, or ``x[t]`` for an identity output).
-    ``expert_out`` is fp32, or in the dtype of ``x``."""
+    ``expert_out`` is fp32, or in the dtype of ``x``.  ``assign``: the sums replace the rows of ``residual``."""
     _require(residual, "residual", torch.float32, 2)
     _require(expert_out, "expert_out", ndim=2)
     _require(x, "x", ndim=2)
@@ -1114,7 +1115,7 @@ def moe_combine(residual: torch.Tensor, expert_out: torch.Tensor, x: torch.Tenso
     if x.shape != (n, H) or expert_out.shape != (table.n_pairs, H) or ids.numel() != table.n_pairs:
         raise KernelError("moe_combine sizes disagree")
     args = _CombineArgs(_ptr(residual), _ptr(expert_out), _ptr(x), _ptr(ids), _ptr(weights), _ptr(table.pos), n, H,
-                        table.top, table.n_experts, 0 if expert_out.dtype == torch.float32 else 1)
+                        table.top, table.n_experts, 0 if expert_out.dtype == torch.float32 else 1, 1 if assign else 0)
     lib = load_library("moe")
     _check(lib.odi_moe_combine(byref(args), c_int(dtype_code(x.dtype)), _stream()), "moe_combine")
 
@@ -1279,6 +1280,29 @@ def rmsnorm_add(hidden: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps
         raise KernelError("rmsnorm_add sizes disagree")
     lib = load_library("capped")
     _check(lib.odi_rmsnorm_add(_ptr(hidden), _ptr(y), _ptr(weight), c_int(n), c_int(H), c_float(eps), _stream()), "rmsnorm_add")
+
+
+def rmsnorm_add_norm(hidden: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, next_weight: torch.Tensor,
+                     next_eps: float, out: torch.Tensor) -> bool:
+    """:func:`rmsnorm_add` followed by the norm of the sum for the next sublayer, in one pass over the row:
+    hidden[t] += y[t] * rsqrt(mean(y[t]^2) + eps) * weight, then out[t] = cast(hidden[t] * rsqrt(mean(hidden[t]^2)
+    + next_eps) * next_weight) (scaled in fp32, one rounding).  Returns False, having done nothing, for widths the
+    fused kernel does not take (no multiple of 4, or above 8,192)."""
+    _require(hidden, "hidden", torch.float32, 2)
+    _require(y, "y", torch.float32, 2)
+    _require(weight, "weight", torch.float32, 1)
+    _require(next_weight, "next_weight", torch.float32, 1)
+    _require(out, "out", ndim=2)
+    n, H = hidden.shape
+    if y.shape != (n, H) or weight.numel() != H or next_weight.numel() != H or out.shape != (n, H):
+        raise KernelError("rmsnorm_add_norm sizes disagree")
+    lib = load_library("capped")
+    code = lib.odi_rmsnorm_add_norm(_ptr(hidden), _ptr(y), _ptr(weight), c_float(eps), _ptr(next_weight), c_float(next_eps),
+                                    _ptr(out), c_int(n), c_int(H), c_int(dtype_code(out.dtype)), _stream())
+    if code == ODI_ERR_UNSUPPORTED:
+        return False
+    _check(code, "rmsnorm_add_norm")
+    return True
 
 
 def gated_row_add(acc: torch.Tensor, y: torch.Tensor, x: torch.Tensor, gate: torch.Tensor) -> None:

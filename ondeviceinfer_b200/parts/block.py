@@ -9,11 +9,6 @@ from ..weights.tensors import TensorDecl
 from .base import Part, build_part, register_part
 
 
-def ops_residual_add(residual, product) -> None:
-    from ..kernels import ops
-    ops.residual_add(residual, product)
-
-
 class PreNormBlock(Part):
     """h += mixer(norm(h)); h += feed_forward(norm(h))  (ondeviceinfer/model.py:49-63); the second half is
     left out for a spec without a feed-forward."""
@@ -56,10 +51,11 @@ class PreNormBlock(Part):
         if pending is not None:
             # a product of the part before is still to be added to the stream: in this norm's pass if it is
             # this stream and the norm knows how, else now
-            ctx.pending_residual_add = None
-            if pending[0] is hidden and getattr(norm, "adds", False):
+            if len(pending) == 2 and pending[0] is hidden and getattr(norm, "adds", False):
+                ctx.pending_residual_add = None
                 return norm(hidden, add=pending[1])
-            ops_residual_add(*pending)
+            from .linear import flush_residual_add
+            flush_residual_add(ctx)
         if known is not None and known[0] is hidden and getattr(norm, "lazy", None) is not None and getattr(consumer, "takes_lazy_norm", False):
             return norm.lazy(hidden, known[1])
         return norm(hidden)
@@ -77,9 +73,14 @@ class SandwichBlock(Part):
     """h += post_norm(mixer(norm(h))); h += post_norm(feed_forward(norm(h))): a norm on both sides of each sublayer.
 
     A sublayer's output is taken in fp32, normed in fp32 and added to the fp32 stream in one kernel
-    (``ops.rmsnorm_add``).  A part that says ``returns_output`` (its ``forward`` returns the output when given no residual) is asked for that;
-    any other part adds into a zeroed fp32 buffer, as the part interface says, so every registered mixer and
-    feed-forward fits."""
+    (``ops.rmsnorm_add``), or, when the next sublayer's norm follows at once, together with that norm
+    (``ops.rmsnorm_add_norm``): the block leaves the add pending on the step's context (``(hidden, output, weight,
+    eps)``), the next norm of this or the following block of this kind finishes it, and the model flushes what is
+    left.  A part that says ``returns_output`` (its ``forward`` returns the output when given no residual) is
+    asked for that; any other part adds into a zeroed fp32 buffer, as the part interface says, so every
+    registered mixer and feed-forward fits."""
+
+    finishes_residual_adds = True     # its norms take over an add that the block before left pending
 
     def __init__(self, spec: SandwichBlockSpec) -> None:
         super().__init__(spec)
@@ -122,14 +123,31 @@ class SandwichBlock(Part):
         call(branch)
         return branch
 
-    def forward(self, hidden, ctx, view) -> None:
+    @staticmethod
+    def _normed(norm, hidden, ctx):
+        """norm(hidden) for the next sublayer; a sublayer output that is still to be normed and added to this
+        stream is finished in the same kernel when the norm allows it, else beforehand."""
         from ..kernels import ops
-        ctx.defers_residual_add = False
-        out = self._branch(self.mixer, hidden, lambda r: self.mixer.forward(self.mixer_norm(hidden), ctx, view, r))
-        ops.rmsnorm_add(hidden, out, self.mixer_post_norm.weight, self.mixer_post_norm.spec.eps)
+        from .linear import flush_residual_add
+        pending = getattr(ctx, "pending_residual_add", None)
+        if (pending is not None and len(pending) == 4 and pending[0] is hidden
+                and getattr(norm.spec, "scale_in_fp32", False) and hasattr(norm, "weight")):
+            out = torch.empty(hidden.shape, dtype=norm.runtime.dtype, device=hidden.device)
+            if ops.rmsnorm_add_norm(hidden, pending[1], pending[2], pending[3], norm.weight, norm.spec.eps, out):
+                ctx.pending_residual_add = None
+                return out
+        flush_residual_add(ctx)
+        return norm(hidden)
+
+    def forward(self, hidden, ctx, view) -> None:
+        ctx.defers_residual_add = False        # the parts' own products add (or return) at once
+        normed = self._normed(self.mixer_norm, hidden, ctx)
+        out = self._branch(self.mixer, hidden, lambda r: self.mixer.forward(normed, ctx, view, r))
+        ctx.pending_residual_add = (hidden, out, self.mixer_post_norm.weight, self.mixer_post_norm.spec.eps)
         if self.ffn is not None:
-            out = self._branch(self.ffn, hidden, lambda r: self.ffn.forward(self.ffn_norm(hidden), ctx, r))
-            ops.rmsnorm_add(hidden, out, self.ffn_post_norm.weight, self.ffn_post_norm.spec.eps)
+            normed = self._normed(self.ffn_norm, hidden, ctx)
+            out = self._branch(self.ffn, hidden, lambda r: self.ffn.forward(normed, ctx, r))
+            ctx.pending_residual_add = (hidden, out, self.ffn_post_norm.weight, self.ffn_post_norm.spec.eps)
         ctx.residual_sumsq = None
 
 

@@ -49,7 +49,7 @@ def _persistent(tokens: int, weight: torch.Tensor, x: torch.Tensor, epi: int, bi
         return False
     if PREFILL_GEMM == "own":
         return True
-    fused = biased or epi in (ops.EPI_SWIGLU, ops.EPI_RESIDUAL)      # a bias is a fused epilogue too
+    fused = biased or epi in (ops.EPI_SWIGLU, ops.EPI_RESIDUAL, ops.EPI_GELU)      # a bias is a fused epilogue too
     return tokens >= (PERSISTENT_MIN_TOKENS_FUSED if fused else PERSISTENT_MIN_TOKENS_PLAIN)
 
 
@@ -249,11 +249,16 @@ def linear(x, weight: torch.Tensor, *, bias: Optional[torch.Tensor] = None, resi
 
 
 def flush_residual_add(ctx) -> None:
-    """Do a residual add that :func:`linear` left pending on ``ctx`` (nothing if there is none)."""
+    """Do a residual add that was left pending on ``ctx`` (nothing if there is none): ``(residual, product)`` from
+    :func:`linear`, or ``(residual, output, weight, eps)`` from a block that norms a sublayer's fp32 output before
+    it adds it (residual += output * rsqrt(mean(output^2) + eps) * weight)."""
     pending = getattr(ctx, "pending_residual_add", None)
     if pending is not None:
         ctx.pending_residual_add = None
-        ops.residual_add(*pending)
+        if len(pending) == 4:
+            ops.rmsnorm_add(*pending)
+        else:
+            ops.residual_add(*pending)
 
 
 # fp32 results of bf16 operands (the logits) are never rounded to bf16 on the way, whatever the number of rows:
@@ -307,6 +312,25 @@ def project_heads(x, weight_qkv: torch.Tensor, head_prep, bias: Optional[torch.T
     if isinstance(x, NormedRows):
         x = x.materialize()
     ops.gemm_prefill_bf16(x, weight_qkv, None, ops.EPI_HEAD_PREP, head_prep=head_prep, bias=bias)
+
+
+def activated_linear(x: torch.Tensor, weight: torch.Tensor, kind: str) -> torch.Tensor:
+    """act(x W^T) in the dtype of ``x``; ``kind`` "gelu_erf" or "gelu_tanh".  The exact GELU of bfloat16 products
+    is the epilogue of the tensor-core kernels (taken on the fp32 sum, one rounding); otherwise the product is
+    followed by the activation kernel."""
+    n, N = x.shape[0], weight.shape[0]
+    if kind == "gelu_erf" and x.dtype == torch.bfloat16:
+        if _own(x, weight):
+            out = torch.empty((n, N), dtype=torch.bfloat16, device=x.device)
+            ops.gemm_bf16(x, weight, out, ops.EPI_GELU)
+            return out
+        if _persistent(n, weight, x, ops.EPI_GELU):
+            out = torch.empty((n, N), dtype=torch.bfloat16, device=x.device)
+            ops.gemm_prefill_bf16(x, weight, out, ops.EPI_GELU)
+            return out
+    out = linear(x, weight)
+    ops.activation(out, out, kind)
+    return out
 
 
 def gated_linear(x, weight_gate_up: torch.Tensor) -> torch.Tensor:

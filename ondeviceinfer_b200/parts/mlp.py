@@ -8,7 +8,7 @@ from ..config.specs import GatedMLPSpec, MLPSpec
 from ..kernels import ops
 from ..weights.tensors import TensorDecl
 from .base import Part, register_part
-from .linear import gated_linear, linear
+from .linear import activated_linear, gated_linear, linear
 
 
 class GatedMLP(Part):
@@ -40,8 +40,8 @@ class GatedMLP(Part):
 
 
 class PlainMLP(Part):
-    """down(act(up(x))) without a gate; the activation (the exact GELU or its tanh form) is taken in fp32 on the
-    rounded product and rounded once."""
+    """down(act(up(x))) without a gate; the activation (the exact GELU or its tanh form) is taken in fp32 and
+    rounded once (in the epilogue of the up product where the tensor-core kernels have it)."""
 
     graph_safe = True
     returns_output = True   # forward(..., residual=None) returns the fp32 output instead of adding it
@@ -63,8 +63,7 @@ class PlainMLP(Part):
 
     def forward(self, x, ctx, residual):
         """Adds to ``residual`` (fp32); with ``residual`` None returns the output as a new fp32 tensor."""
-        act = linear(x, self.w_up)
-        ops.activation(act, act, self.spec.activation)
+        act = activated_linear(x, self.w_up, self.spec.activation)
         if residual is None:
             return linear(act, self.w_down, out_dtype=torch.float32)
         linear(act, self.w_down, residual=residual, track=ctx)

@@ -20,7 +20,7 @@ from ..config.specs import TableExpertsSpec
 from ..kernels import ops
 from ..weights.tensors import TensorDecl
 from .base import Part, register_part
-from .linear import linear
+from .linear import activated_linear, linear
 from .routed_experts import ROWS_PER_EXPERT_FOR_TENSOR_CORES
 
 GROUPED_EPILOGUE = {"gelu_erf": ops.GROUPED_GELU_ERF, "gelu_tanh": ops.GROUPED_GELU_TANH}
@@ -28,6 +28,7 @@ GROUPED_EPILOGUE = {"gelu_erf": ops.GROUPED_GELU_ERF, "gelu_tanh": ops.GROUPED_G
 
 class TableExperts(Part):
     graph_safe = True
+    returns_output = True   # forward(..., residual=None) returns the fp32 output instead of adding it
     _library_groups = True      # until the vendor library's grouped product has refused once
 
     def __init__(self, spec: TableExpertsSpec) -> None:
@@ -62,7 +63,8 @@ class TableExperts(Part):
             self.w_shared_down = fetch.matrix(s.prefix + "shared.down")
             self.w_shared_gate = fetch.matrix(s.prefix + "shared.sg").reshape(-1).contiguous() if s.shared_gated else None
 
-    def forward(self, x, ctx, residual) -> None:
+    def forward(self, x, ctx, residual):
+        """Adds to ``residual`` (fp32); with ``residual`` None returns the output as a new fp32 tensor."""
         s = self.spec
         n, dev = x.shape[0], x.device
         ids = torch.empty((n, s.top_k), dtype=torch.int32, device=dev)
@@ -81,16 +83,19 @@ class TableExperts(Part):
             expert_out = torch.empty((table.n_pairs, s.hidden_size), dtype=torch.float32, device=dev)
             ops.grouped_gemm_routed(x, self.w_up, act, table, gather=True, epi=GROUPED_EPILOGUE[s.activation])
             ops.grouped_gemm_routed(act, self.w_down, expert_out, table, gather=False, epi=ops.GROUPED_STORE_F32)
-        ops.moe_combine(residual, expert_out, x, ids, weights, table)
+        assign = residual is None
+        if assign:
+            residual = torch.empty((n, s.hidden_size), dtype=torch.float32, device=dev)
+        ops.moe_combine(residual, expert_out, x, ids, weights, table, assign=assign)
         if s.shared_size > 0:
-            shared = linear(x, self.w_shared_up)
-            ops.activation(shared, shared, s.activation)
+            shared = activated_linear(x, self.w_shared_up, s.activation)
             if self.w_shared_gate is None:
                 linear(shared, self.w_shared_down, residual=residual)
             else:
                 ops.gated_row_add(residual, linear(shared, self.w_shared_down, out_dtype=torch.float32), x, self.w_shared_gate)
         if ctx is not None:
             ctx.residual_sumsq = None
+        return residual if assign else None
 
     def _library_products(self, x, table, act):
         """bfloat16 prompts: the experts' products by the vendor library's grouped product over rows gathered side

@@ -18,6 +18,7 @@ import ondeviceinfer_b200 as odi
 import plain_nulalorn as plain
 from helpers import assert_logits_close, write_model_folder
 from ondeviceinfer_b200.kernels import ops
+from ondeviceinfer_b200.parts.linear import flush_residual_add
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
@@ -249,6 +250,16 @@ def test_activation_norm_and_add_gate_and_cap(dtype):
     h = hidden.clone().cuda()
     ops.rmsnorm_add(h, y.cuda(), w.cuda(), 1e-3)
     assert (h.cpu().double() - (hidden.double() + plain.rms_norm(y.double(), w.double(), 1e-3))).abs().max() < 1e-5
+    for width in (50, 48, 2048):                # element by element; four lanes at a time; several per thread
+        hid, ys = torch.randn(5, width, generator=g), torch.randn(5, width, generator=g) * 2
+        w1, w2 = torch.randn(width, generator=g), torch.randn(width, generator=g)
+        h, fused = hid.clone().cuda(), torch.empty((5, width), dtype=dtype, device="cuda")
+        want_h = hid.double() + plain.rms_norm(ys.double(), w1.double(), 1e-3)
+        if ops.rmsnorm_add_norm(h, ys.cuda(), w1.cuda(), 1e-3, w2.cuda(), 1e-5, fused):
+            assert (h.cpu().double() - want_h).abs().max() < 1e-5
+            assert (fused.cpu().double() - plain.rms_norm(want_h, w2.double(), 1e-5)).abs().max() < tol * 3
+        else:
+            assert width % 4 != 0 and torch.equal(h.cpu(), hid)
     # a shared expert's output times sigmoid(sg . x)
     acc, sg = torch.randn(9, 30, generator=g), (torch.randn(50, generator=g) * 0.3).to(dtype)
     for y_dtype in {torch.float32, dtype}:
@@ -327,6 +338,7 @@ def test_residual_stream_after_every_layer_run(dtype, tmp_path_factory):
         for block, original in zip(blocks, originals):
             def record(hidden, ctx, view, original=original):
                 result = original(hidden, ctx, view)
+                flush_residual_add(ctx)           # the block leaves its last add to the next norm
                 seen.append(hidden.clone())
                 return result
             block.forward = record
