@@ -99,9 +99,100 @@ __global__ void rot_unit_prep_kernel(RotUnitArgs a) {
   }
 }
 
+// bf16 heads whose width is a multiple of 4 (d == d_store): a lane holds four neighbouring lanes of the head per
+// step of 128, so both members of a rotated pair sit in one thread, and every access is 8 bytes wide.  A warp
+// takes `heads_per_warp` heads of one token one after the other.  Same arithmetic as rot_unit_prep_kernel.
+template <int MAXP4>
+__global__ void rot_unit_prep_vec_kernel(RotUnitArgs a, int heads_per_warp) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int heads = a.nq + (a.write_kv ? 2 * a.nkv : 0);
+  const int groups = (heads + heads_per_warp - 1) / heads_per_warp;
+  const long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long)a.n_tokens * groups) return;
+  const int t = (int)(item / groups), h_begin = (int)(item % groups) * heads_per_warp;
+  const int d = a.d, half = a.rot_dim >> 1;
+  const size_t row = (size_t)(a.nq + a.nkv) * d + (size_t)a.nkv * a.dv;
+  const bf16* base = (const bf16*)a.qkv + (size_t)t * row;
+  const int pos = a.tok_pos[t];
+  size_t at = 0;
+  if (a.write_kv) {
+    const int s = a.tok_seq[t];
+    const int page = a.page_ids[a.page_start[s] + page_slot_of(pos, a.page_size, a.ring_pages)];
+    at = (size_t)page * a.nkv * a.page_size + (pos % a.page_size);
+  }
+  for (int h = h_begin; h < min(heads, h_begin + heads_per_warp); ++h) {
+    const int kind = h < a.nq ? 0 : (h < a.nq + a.nkv ? 1 : 2);
+    if (kind == 2) {
+      const int hk = h - a.nq - a.nkv;
+      const bf16* src = base + (size_t)(a.nq + a.nkv) * d + (size_t)hk * a.dv;
+      bf16* dst = (bf16*)a.v_pool + (at + (size_t)hk * a.page_size) * a.dv;
+      for (int i = lane; i < a.dv; i += 32) dst[i] = src[i];
+      continue;
+    }
+    const int hk = h - a.nq;
+    const bf16* src = base + (size_t)h * d;         // q heads, then k heads, follow one another in the row
+    bf16* dst = kind == 0 ? (bf16*)a.q_out + ((size_t)t * a.nq + h) * d
+                          : (bf16*)a.k_pool + (at + (size_t)hk * a.page_size) * d;
+    float x[MAXP4][4];
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < MAXP4; ++r) {
+      const int i = 4 * lane + 128 * r;
+      if (i < d) {
+        const uint2 raw = *(const uint2*)(src + i);
+        const float2 lo = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x), hi = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
+        x[r][0] = lo.x; x[r][1] = lo.y; x[r][2] = hi.x; x[r][3] = hi.y;
+        if (a.cos_t != nullptr && i < a.rot_dim) {
+#pragma unroll
+          for (int pr = 0; pr < 2; ++pr) {
+            if (i + 2 * pr < a.rot_dim) {
+              const float cs = a.cos_t[(size_t)t * half + (i >> 1) + pr], sn = a.sin_t[(size_t)t * half + (i >> 1) + pr];
+              const float u = x[r][2 * pr], v = x[r][2 * pr + 1];
+              x[r][2 * pr] = fmaf(-v, sn, u * cs);
+              x[r][2 * pr + 1] = fmaf(u, sn, v * cs);
+            }
+          }
+        }
+        ss += x[r][0] * x[r][0] + x[r][1] * x[r][1] + x[r][2] * x[r][2] + x[r][3] * x[r][3];
+      } else {
+        x[r][0] = x[r][1] = x[r][2] = x[r][3] = 0.f;
+      }
+    }
+    float inv = 1.f;
+    if (a.unit) {
+      ss = warp_sum(ss);
+      inv = 1.0f / sqrtf(ss / (float)d + a.eps);
+    }
+#pragma unroll
+    for (int r = 0; r < MAXP4; ++r) {
+      const int i = 4 * lane + 128 * r;
+      if (i < d) {
+        uint2 packed;
+        *(__nv_bfloat162*)&packed.x = __floats2bfloat162_rn(x[r][0] * inv, x[r][1] * inv);
+        *(__nv_bfloat162*)&packed.y = __floats2bfloat162_rn(x[r][2] * inv, x[r][3] * inv);
+        *(uint2*)(dst + i) = packed;
+      }
+    }
+  }
+}
+
 extern "C" int odi_rot_unit_prep(const RotUnitArgs* args, int dtype, cudaStream_t stream) {
   RotUnitArgs a = *args;
   if (a.n_tokens <= 0) return 0;
+  if (dtype == 1 && a.d == a.d_store && a.d % 4 == 0 && a.d <= 512 && a.d > 0 && a.dv > 0 && !(a.rot_dim & 1) && a.rot_dim <= a.d &&
+      ((uintptr_t)a.qkv | (uintptr_t)a.q_out | (uintptr_t)a.k_pool) % 8 == 0 && (a.nkv * a.dv) % 4 == 0) {
+    const int heads = a.nq + (a.write_kv ? 2 * a.nkv : 0);
+    // few tokens: a warp per head for parallelism; many tokens: a warp takes a quarter of a token's heads
+    const int hpw = a.n_tokens >= 256 ? (heads + 3) / 4 : 1;
+    const long warps = (long)a.n_tokens * ((heads + hpw - 1) / hpw);
+    const int vblocks = (int)((warps + 3) / 4);
+    if (a.d <= 128) odi_rc = launch_pdl((rot_unit_prep_vec_kernel<1>), dim3(vblocks), dim3(128), 0, stream, a, hpw);
+    else if (a.d <= 256) odi_rc = launch_pdl((rot_unit_prep_vec_kernel<2>), dim3(vblocks), dim3(128), 0, stream, a, hpw);
+    else odi_rc = launch_pdl((rot_unit_prep_vec_kernel<4>), dim3(vblocks), dim3(128), 0, stream, a, hpw);
+    return launch_status();
+  }
   if (a.d_store > 512 || a.d <= 0 || a.d_store < a.d || a.dv <= 0 || (a.rot_dim & 1) || a.rot_dim > a.d) return ODI_ERR_UNSUPPORTED;
   const int heads = a.nq + (a.write_kv ? 2 * a.nkv : 0);
   const long items = (long)a.n_tokens * heads;
