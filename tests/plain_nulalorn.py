@@ -243,6 +243,18 @@ SHARP = {
                                rot={"base": 10000.0, "dims": 8}, mlp={"kind": "dense", "ff": 48})],
 }
 
+# WIDE_HEADS: key and value heads of 64 lanes (the sizes of the kernel that keeps scores in tensor memory), a window
+# that crosses pages, a second layer that sees every key.
+WIDE_HEADS = {
+    "architecture": "Nulalorn", "vocab": 70, "width": 64, "norm": {"eps": 1e-5}, "logit_softcap": 15.0,
+    "loop": {"start": 0, "stop": 2, "times": 2},
+    "layers": [attention_layer(heads=2, kv_heads=1, dim=64, vdim=64, scale=0.2, softcap=12.0, window=100,
+                               rot={"base": 10000.0, "dims": 32, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 256}},
+                               mlp=moe(4, 2, 32, shared=32)),
+               attention_layer(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.15, rot={"base": 500.0, "dims": 64},
+                               mlp={"kind": "dense", "ff": 96})],
+}
+
 # NOLOOP: no loop at all and nothing optional.
 PLAIN_STACK = {
     "architecture": "Nulalorn", "vocab": 29, "width": 24, "norm": {"eps": 1e-5},

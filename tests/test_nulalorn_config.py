@@ -14,7 +14,7 @@ from ondeviceinfer_b200.parts.position import scaled_frequencies
 from ondeviceinfer_b200.registry import config_from_dict
 from ondeviceinfer_b200.weights.tensors import RandomSource
 
-CONFIGS = [plain.TINY_A, plain.TINY_B, plain.TINY_C, plain.SHARP, plain.PLAIN_STACK] + [plain.random_config(s) for s in range(8)]
+CONFIGS = [plain.TINY_A, plain.TINY_B, plain.TINY_C, plain.SHARP, plain.PLAIN_STACK, plain.WIDE_HEADS] + [plain.random_config(s) for s in range(8)]
 
 
 @pytest.mark.parametrize("cfg", CONFIGS)

@@ -23,7 +23,7 @@ from ondeviceinfer_b200.parts.linear import flush_residual_add
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
 CONFIGS = {"A": (plain.TINY_A, 31), "B": (plain.TINY_B, 32), "C": (plain.TINY_C, 33), "sharp": (plain.SHARP, 34),
-           "bare": (plain.PLAIN_STACK, 35)}
+           "bare": (plain.PLAIN_STACK, 35), "wide": (plain.WIDE_HEADS, 36)}
 _MODELS, _PLAIN = {}, {}
 
 
@@ -311,7 +311,7 @@ def test_table_routed_experts_against_a_loop_over_tokens(dtype, tokens, experts,
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C", "bare"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "bare", "wide"])
 def test_whole_prompts_and_their_first_tokens(case, dtype, tmp_path_factory):
     model = engine(case, dtype, tmp_path_factory)
     cfg = CONFIGS[case][0]
@@ -354,7 +354,7 @@ def test_residual_stream_after_every_layer_run(dtype, tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "wide"])
 def test_prompt_then_single_tokens_over_page_and_window_borders(case, dtype, tmp_path_factory):
     model = engine(case, dtype, tmp_path_factory)
     cfg = CONFIGS[case][0]
@@ -372,7 +372,7 @@ def test_prompt_then_single_tokens_over_page_and_window_borders(case, dtype, tmp
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "C"])
+@pytest.mark.parametrize("case", ["A", "C", "wide"])
 def test_portions_of_several_sizes_down_to_two_tokens(case, dtype, tmp_path_factory):
     model = engine(case, dtype, tmp_path_factory)
     cfg = CONFIGS[case][0]
@@ -388,7 +388,7 @@ def test_portions_of_several_sizes_down_to_two_tokens(case, dtype, tmp_path_fact
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B"])
+@pytest.mark.parametrize("case", ["A", "B", "wide"])
 def test_unequal_batches_on_slots_and_pages_used_again(case, dtype, tmp_path_factory):
     model = engine(case, dtype, tmp_path_factory)
     cfg = CONFIGS[case][0]
