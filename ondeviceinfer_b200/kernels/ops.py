@@ -61,7 +61,13 @@ def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+# the raw handle of the current stream without building a Stream object (several microseconds a launch)
+_raw_current_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    if _raw_current_stream is not None:
+        return c_void_p(_raw_current_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
