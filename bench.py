@@ -611,7 +611,7 @@ def _nulalorn_config(width, heads, kv_heads, dim, vdim, window, experts, top, ff
              "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     moe = {"kind": "moe", "expert": {"ff": ff}, "shared": {"ff": shared_ff}, "router": {"experts": experts, "top": top}}
     layer = lambda mlp: {"type": "attention", "mixer": mixer, "mlp": mlp}
-    return {"architecture": "Nulalorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+    return {"architecture": "Nulalorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 40.0,
             "loop": {"start": 1, "stop": 4, "times": 2},
             "layers": [layer({"kind": "dense", "ff": dense_ff})] + [layer(moe) for _ in range(3)]}
 
