@@ -467,6 +467,24 @@ def test_sharp_attention_finds_far_keys_in_prompts_and_in_decoding(dtype, tmp_pa
         assert float((off_by_one[300:] - want[300:]).abs().max()) > 0.05
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompts_are_cut_and_go_round_the_ring(dtype, tmp_path_factory):
+    """A prompt of 700 tokens on a cache whose passes take 256 tokens of a sequence: three portions, the third one
+    written over the ring's oldest pages (window 100: seven pages), beside a short request in the same step; heads
+    of 64 lanes, so bfloat16 takes the kernel that keeps scores in tensor memory."""
+    model = engine("wide", dtype, tmp_path_factory)
+    long, short = plain.random_prompts(plain.WIDE_HEADS, [700, 40], 12)
+    cache = model.make_cache(max_tokens=1024, max_seqs=2)
+    assert cache.max_step_tokens == 256 and any(0 < group.ring_pages * 64 < 700 for group in cache.kv_groups)
+    slots = [cache.alloc(), cache.alloc()]
+    got = model.step(cache, slots, [long, short], "all")
+    close(got[:700], expected("wide", long), dtype, "long prompt in portions")
+    close(got[700:], expected("wide", short), dtype, "short prompt beside it")
+    more = plain.random_prompts(plain.WIDE_HEADS, [30], 13)[0]
+    rows = [model.step(cache, slots[:1], [[t]], "last") for t in more]
+    close(torch.cat(rows), expected("wide", long + more)[700:], dtype, "single tokens after the long prompt")
+
+
 def test_long_decoding_wraps_the_ring_of_a_windowed_cache(tmp_path_factory):
     """Windows of 7 and 3 keep rings of a few pages per sequence; 700 single-token steps go round them twice."""
     model = engine("A", "float32", tmp_path_factory)
