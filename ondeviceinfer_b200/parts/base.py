@@ -47,6 +47,14 @@ residual add pending (``ctx.pending_residual_add``) and the block's next norm do
 the next such block or by the model.  Whoever calls such a block directly finishes with
 ``parts.linear.flush_residual_add(ctx)``.  A block that knows nothing of this never sees a pending add.
 
+Also optional, for blocks that norm a sublayer's output before they add it (``parts/block.py: SandwichBlock``): a mixer
+or feed-forward that says ``returns_output = True`` returns its fp32 output [tokens, hidden] when ``residual`` is None
+instead of adding it (any other part is handed a zeroed buffer as its residual); such a block leaves its last add
+pending as ``ctx.pending_residual_add = (residual, output, weight, eps)``, which the next norm or
+``flush_residual_add`` finishes as residual += output * rsqrt(mean(output^2) + eps) * weight.  A block's ``forward`` may
+return a new residual stream instead of changing the one it was given (the model goes on with it), and a block that
+says ``reads_embedding = True`` finds the embedding's output as ``ctx.embedded``.
+
 Also optional: a mixer whose single-token kernel cuts each sequence's keys among several blocks may ask the
 context how (``ctx.key_splits(blocks_per_cut) -> (tiles_per_split, splits)``): the number of 64-key tiles
 that a block takes, as one int32 on the device that follows the step's sequences (also under graph replay,
