@@ -17,6 +17,7 @@
 // TM = 64 (4 x 4 outputs a thread) or 16 (1 x 4), chosen by the caller from the rows a group has; for groups
 // of a few rows there is a form that streams the weights through registers only (grouped_gemv_kernel).
 #include "common.cuh"
+#include <type_traits>
 
 #define TN 64
 
@@ -287,6 +288,139 @@ grouped_gemv_kernel(GroupedArgs a) {
   }
 }
 
+// The same for bf16 with the weights streamed through shared memory by cp.async: every lane keeps GS_STAGES - 1
+// requests of 16 bytes per weight row in flight (each lane later reads exactly the bytes it asked for, so the ring needs
+// no barrier), which decouples the stream from the arithmetic: 96 KB on their way per SM instead of what the
+// registers of the form above can hold.  The input rows wait in shared memory as bf16.  Same sums in the same order
+// per lane; the order over the lanes is the same fixed tree.
+#define GS_STAGES 4
+#define GS_CHUNK 256          // k per stage: 32 lanes x 8
+__device__ __forceinline__ void gs_cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void gs_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void gs_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void gs_unpack8(const uint4& raw, float* out) {
+  const __nv_bfloat162* h = (const __nv_bfloat162*)&raw;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); out[2 * i] = f.x; out[2 * i + 1] = f.y; }
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(256, 1)
+grouped_gemv_stream_kernel(GroupedArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) uint8_t gs_smem[];
+  bf16* xs = (bf16*)gs_smem;                                   // [GV_ROWS][K]
+  __shared__ int arow[GV_ROWS];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint8_t* ring = gs_smem + (size_t)GV_ROWS * a.K * 2 + (size_t)warp * GS_STAGES * 8 * 512;   // [stage][row j][512 bytes]
+  int group, row0, rows;
+  if (a.tile_group != nullptr) {
+    const int t = blockIdx.x;
+    if (t >= a.n_tiles[0]) return;
+    group = a.tile_group[t]; row0 = a.tile_row0[t]; rows = a.tile_rows[t];
+  } else {
+    group = blockIdx.z; row0 = blockIdx.x * GV_ROWS; rows = min(GV_ROWS, a.M - row0);
+  }
+  if (tid < GV_ROWS) {
+    int r = -1;
+    if (tid < rows) r = a.row_index != nullptr ? a.row_index[row0 + tid] / a.index_div : row0 + tid;
+    arow[tid] = r;
+  }
+  const bf16* A = (const bf16*)a.A + (a.tile_group != nullptr ? 0 : (size_t)group * a.a_group_off);
+  const bf16* W = (const bf16*)a.W + (size_t)group * a.w_group_stride;
+  const int n0 = blockIdx.y * (GATED ? 32 : 64);
+  const bf16* wrow[8];
+  bool wlive[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int n = GATED ? n0 + warp * 4 + (j >> 1) : n0 + warp * 8 + j;
+    wlive[j] = n < a.N;
+    wrow[j] = W + (size_t)((GATED && (j & 1)) ? a.N + n : n) * a.ldw;
+  }
+  const int n_chunks = (a.K + GS_CHUNK - 1) / GS_CHUNK;
+  auto issue = [&](int c) {
+    const int k = c * GS_CHUNK + lane * 8;
+    if (c < n_chunks && k < a.K) {
+      uint8_t* st = ring + (size_t)(c % GS_STAGES) * 8 * 512 + lane * 16;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (wlive[j]) gs_cp_async16(st + j * 512, wrow[j] + k);
+    }
+    gs_commit();                     // one group per chunk, empty or not: the count stays uniform
+  };
+#pragma unroll
+  for (int c = 0; c < GS_STAGES - 1; ++c) issue(c);     // weights are written by no kernel: they may start at once
+  __syncthreads();                                      // arow
+  for (int i = tid * 8; i < GV_ROWS * a.K; i += 256 * 8) {
+    const int r = i / a.K, k = i % a.K;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (arow[r] >= 0) v = *(const uint4*)(A + (size_t)arow[r] * a.lda + k);
+    *(uint4*)(xs + i) = v;
+  }
+  __syncthreads();
+  float acc[8][GV_ROWS] = {};
+  // The arithmetic follows the rows the tile really has (a single-token step gives most experts one or two):
+  // the instructions of four rows for every weight byte would cost as much time as the bytes themselves.
+  auto walk = [&](auto nr_tag) {
+    constexpr int NR = decltype(nr_tag)::value;
+    for (int c = 0; c < n_chunks; ++c) {
+      issue(c + GS_STAGES - 1);
+      gs_wait<GS_STAGES - 1>();        // this lane's requests for chunk c have landed
+      const int k = c * GS_CHUNK + lane * 8;
+      if (k < a.K) {
+        float x[NR][8];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) gs_unpack8(*(const uint4*)(xs + (size_t)r * a.K + k), x[r]);
+        const uint8_t* st = ring + (size_t)(c % GS_STAGES) * 8 * 512 + lane * 16;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (!wlive[j]) continue;
+          float w[8];
+          gs_unpack8(*(const uint4*)(st + j * 512), w);
+#pragma unroll
+          for (int r = 0; r < NR; ++r)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[j][r] = fmaf(w[e], x[r][e], acc[j][r]);
+        }
+      }
+    }
+  };
+  if (rows <= 1) walk(std::integral_constant<int, 1>{});
+  else if (rows == 2) walk(std::integral_constant<int, 2>{});
+  else walk(std::integral_constant<int, GV_ROWS>{});
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int r = 0; r < GV_ROWS; ++r) acc[j][r] = warp_sum(acc[j][r]);
+  if (lane != 0) return;
+#pragma unroll
+  for (int r = 0; r < GV_ROWS; ++r) {
+    if (r >= rows) continue;
+    const size_t crow = (size_t)(row0 + r) * a.ldc + (a.tile_group != nullptr ? 0 : (size_t)group * a.c_group_off);
+    if (GATED) {
+#pragma unroll
+      for (int f = 0; f < 4; ++f) {
+        const int n = n0 + warp * 4 + f;
+        if (n >= a.N) continue;
+        const float g = fminf(acc[2 * f][r], a.limit);
+        const float u = fminf(fmaxf(acc[2 * f + 1][r], -a.limit), a.limit);
+        ((bf16*)a.C)[crow + n] = from_f<bf16>(g / (1.f + expf(-a.alpha * g)) * (u + 1.f));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int n = n0 + warp * 8 + j;
+        if (n >= a.N) continue;
+        if (a.epi == 1) ((float*)a.C)[crow + n] = acc[j][r];
+        else ((bf16*)a.C)[crow + n] = from_f<bf16>(grouped_act(acc[j][r], a.epi));
+      }
+    }
+  }
+}
+
 // max_tiles: with a tile table, the most tiles the table can hold (the grid's width); tm: 16 or 64 (the
 // table must have been built for the same tm); tm = 4 asks for the form for few rows, which needs aligned
 // operands (odi_grouped_gemm_takes_few_rows says whether it can run).
@@ -316,6 +450,17 @@ extern "C" int odi_grouped_gemm(const GroupedArgs* args, int max_tiles, int tm, 
       if (grid.z > 65535) return ODI_ERR_UNSUPPORTED;
     }
     if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
+    const size_t stream_smem = (size_t)GV_ROWS * a.K * 2 + (size_t)8 * GS_STAGES * 8 * 512;
+    if (dtype == 1 && stream_smem <= 200 * 1024 && getenv("ODI_GROUPED_GEMV") == nullptr) {
+      // bf16: the weights through a cp.async ring (ODI_GROUPED_GEMV=registers keeps the form above)
+#define ODI_GS(G) \
+      do { cudaError_t e = cudaFuncSetAttribute(grouped_gemv_stream_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stream_smem); \
+           if (e != cudaSuccess) return (int)e; \
+           odi_rc = launch_pdl((grouped_gemv_stream_kernel<G>), grid, dim3(256), stream_smem, stream, a); } while (0)
+      if (a.epi == 2) ODI_GS(true); else ODI_GS(false);
+#undef ODI_GS
+      return launch_status();
+    }
     const size_t smem = (size_t)GV_ROWS * a.K * sizeof(float);
 #define ODI_GV(T, G) \
     do { cudaError_t e = cudaFuncSetAttribute(grouped_gemv_kernel<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
