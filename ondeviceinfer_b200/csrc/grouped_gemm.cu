@@ -17,6 +17,8 @@
 // TM = 64 (4 x 4 outputs a thread) or 16 (1 x 4), chosen by the caller from the rows a group has; for groups
 // of a few rows there is a form that streams the weights through registers only (grouped_gemv_kernel).
 #include "common.cuh"
+#include <algorithm>
+#include <cstring>
 #include <type_traits>
 
 #define TN 64
@@ -288,12 +290,9 @@ grouped_gemv_kernel(GroupedArgs a) {
   }
 }
 
-// The same for bf16 with the weights streamed through shared memory by cp.async: every lane keeps GS_STAGES - 1
-// requests of 16 bytes per weight row in flight (each lane later reads exactly the bytes it asked for, so the ring needs
-// no barrier), which decouples the stream from the arithmetic: 96 KB on their way per SM instead of what the
-// registers of the form above can hold.  The input rows wait in shared memory as bf16.  Same sums in the same order
-// per lane; the order over the lanes is the same fixed tree.
-#define GS_STAGES 4
+// bf16 with the weights streamed through shared memory by cp.async: every lane keeps several requests of 16 bytes per
+// weight row in flight and later reads exactly the bytes it asked for, so the ring needs no barrier, and the stream
+// is decoupled from the arithmetic: far more bytes on their way per SM than the registers of the form above can hold.
 #define GS_CHUNK 256          // k per stage: 32 lanes x 8
 __device__ __forceinline__ void gs_cp_async16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -306,118 +305,154 @@ __device__ __forceinline__ void gs_unpack8(const uint4& raw, float* out) {
   for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); out[2 * i] = f.x; out[2 * i + 1] = f.y; }
 }
 
-template <bool GATED>
+// Blocks that stay: one block an SM, and every warp on its own walks a list of items (a tile of up to 4 input rows
+// x R weight rows), item after item through one ring of S stages, so that the requests for the next item's first
+// chunks are out before the current item ends and the ring stays full across items.  A stage holds one chunk
+// (256 k) of the R weight rows and of the tile's input rows (each lane asks for, and later reads, its own 16 bytes of
+// every row: no barrier anywhere).  The items of a warp are laid out 32 at a time by its lanes (group, rows and source
+// rows of the tile) in shared memory.  Sums per lane in the same order as the forms above, the same tree over lanes.
+template <bool GATED, int R, int S>
 __global__ void __launch_bounds__(256, 1)
-grouped_gemv_stream_kernel(GroupedArgs a) {
+grouped_gemv_walk_kernel(GroupedArgs a, int row_tiles) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) uint8_t gs_smem[];
-  bf16* xs = (bf16*)gs_smem;                                   // [GV_ROWS][K]
-  __shared__ int arow[GV_ROWS];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  uint8_t* ring = gs_smem + (size_t)GV_ROWS * a.K * 2 + (size_t)warp * GS_STAGES * 8 * 512;   // [stage][row j][512 bytes]
-  int group, row0, rows;
-  if (a.tile_group != nullptr) {
-    const int t = blockIdx.x;
-    if (t >= a.n_tiles[0]) return;
-    group = a.tile_group[t]; row0 = a.tile_row0[t]; rows = a.tile_rows[t];
-  } else {
-    group = blockIdx.z; row0 = blockIdx.x * GV_ROWS; rows = min(GV_ROWS, a.M - row0);
-  }
-  if (tid < GV_ROWS) {
-    int r = -1;
-    if (tid < rows) r = a.row_index != nullptr ? a.row_index[row0 + tid] / a.index_div : row0 + tid;
-    arow[tid] = r;
-  }
-  const bf16* A = (const bf16*)a.A + (a.tile_group != nullptr ? 0 : (size_t)group * a.a_group_off);
-  const bf16* W = (const bf16*)a.W + (size_t)group * a.w_group_stride;
-  const int n0 = blockIdx.y * (GATED ? 32 : 64);
-  const bf16* wrow[8];
-  bool wlive[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int n = GATED ? n0 + warp * 4 + (j >> 1) : n0 + warp * 8 + j;
-    wlive[j] = n < a.N;
-    wrow[j] = W + (size_t)((GATED && (j & 1)) ? a.N + n : n) * a.ldw;
-  }
+  constexpr int STAGE = (R + GV_ROWS) * 512;
+  constexpr int FEATS = GATED ? R / 2 : R;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint8_t* ring = gs_smem + (size_t)warp * S * STAGE + lane * 16;
+  int* meta = (int*)(gs_smem + (size_t)8 * S * STAGE) + warp * 32 * 8;
+  const bool table = a.tile_group != nullptr;
+  const int ncg = (a.N + FEATS - 1) / FEATS;
+  const long long n_items = (long long)(table ? a.n_tiles[0] : row_tiles * a.groups) * ncg;
+  const int nw = gridDim.x * 8, gw = warp * gridDim.x + blockIdx.x;       // neighbouring items on different SMs
+  if (gw >= n_items) return;
+  const int my_items = (int)((n_items - gw + nw - 1) / nw);
   const int n_chunks = (a.K + GS_CHUNK - 1) / GS_CHUNK;
-  auto issue = [&](int c) {
-    const int k = c * GS_CHUNK + lane * 8;
-    if (c < n_chunks && k < a.K) {
-      uint8_t* st = ring + (size_t)(c % GS_STAGES) * 8 * 512 + lane * 16;
+  const int kl = lane * 8;
+  for (int base = 0; base < my_items; base += 32) {
+    const int cnt = min(32, my_items - base);
+    if (lane < cnt) {
+      const long long item = gw + (long long)(base + lane) * nw;
+      const int t = (int)(item / ncg);
+      int group, row0, rows;
+      if (table) { group = a.tile_group[t]; row0 = a.tile_row0[t]; rows = a.tile_rows[t]; }
+      else { group = t / row_tiles; row0 = (t % row_tiles) * GV_ROWS; rows = min(GV_ROWS, a.M - row0); }
+      int* m = meta + lane * 8;
+      m[0] = group; m[1] = row0; m[2] = rows; m[3] = (int)(item % ncg);
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (wlive[j]) gs_cp_async16(st + j * 512, wrow[j] + k);
+      for (int r = 0; r < GV_ROWS; ++r)
+        m[4 + r] = r < rows ? (a.row_index != nullptr ? a.row_index[row0 + r] / a.index_div : row0 + r) : -1;
     }
-    gs_commit();                     // one group per chunk, empty or not: the count stays uniform
-  };
+    __syncwarp();
+    // the requesting side: item and chunk of the next request, and the item's addresses
+    int is_it = 0, is_chunk = 0, is_stage = 0, is_n0 = 0;
+    const bf16* is_w = nullptr;
+    const bf16* is_x[GV_ROWS] = {};
+    auto issue = [&]() {
+      if (is_it < cnt) {
+        if (is_chunk == 0) {
+          const int* m = meta + is_it * 8;
+          const int group = m[0];
+          is_w = (const bf16*)a.W + (size_t)group * a.w_group_stride;
+          is_n0 = m[3] * FEATS;
+          const bf16* A = (const bf16*)a.A + (table ? 0 : (size_t)group * a.a_group_off);
 #pragma unroll
-  for (int c = 0; c < GS_STAGES - 1; ++c) issue(c);     // weights are written by no kernel: they may start at once
-  __syncthreads();                                      // arow
-  for (int i = tid * 8; i < GV_ROWS * a.K; i += 256 * 8) {
-    const int r = i / a.K, k = i % a.K;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (arow[r] >= 0) v = *(const uint4*)(A + (size_t)arow[r] * a.lda + k);
-    *(uint4*)(xs + i) = v;
-  }
-  __syncthreads();
-  float acc[8][GV_ROWS] = {};
-  // The arithmetic follows the rows the tile really has (a single-token step gives most experts one or two):
-  // the instructions of four rows for every weight byte would cost as much time as the bytes themselves.
-  auto walk = [&](auto nr_tag) {
-    constexpr int NR = decltype(nr_tag)::value;
-    for (int c = 0; c < n_chunks; ++c) {
-      issue(c + GS_STAGES - 1);
-      gs_wait<GS_STAGES - 1>();        // this lane's requests for chunk c have landed
-      const int k = c * GS_CHUNK + lane * 8;
-      if (k < a.K) {
-        float x[NR][8];
-#pragma unroll
-        for (int r = 0; r < NR; ++r) gs_unpack8(*(const uint4*)(xs + (size_t)r * a.K + k), x[r]);
-        const uint8_t* st = ring + (size_t)(c % GS_STAGES) * 8 * 512 + lane * 16;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (!wlive[j]) continue;
-          float w[8];
-          gs_unpack8(*(const uint4*)(st + j * 512), w);
-#pragma unroll
-          for (int r = 0; r < NR; ++r)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[j][r] = fmaf(w[e], x[r][e], acc[j][r]);
+          for (int r = 0; r < GV_ROWS; ++r) is_x[r] = m[4 + r] >= 0 ? A + (size_t)m[4 + r] * a.lda : nullptr;
         }
+        const int k = is_chunk * GS_CHUNK + kl;
+        if (k < a.K) {
+          uint8_t* st = ring + (size_t)is_stage * STAGE;
+#pragma unroll
+          for (int j = 0; j < R; ++j) {
+            const int n = GATED ? is_n0 + (j >> 1) : is_n0 + j;
+            if (n < a.N) gs_cp_async16(st + j * 512, is_w + (size_t)((GATED && (j & 1)) ? a.N + n : n) * a.ldw + k);
+          }
+#pragma unroll
+          for (int r = 0; r < GV_ROWS; ++r)
+            if (is_x[r] != nullptr) gs_cp_async16(st + (R + r) * 512, is_x[r] + k);
+        }
+        if (++is_chunk == n_chunks) { is_chunk = 0; ++is_it; }
+      }
+      if (++is_stage == S) is_stage = 0;
+      gs_commit();                     // one group per request, empty or not: the count stays uniform
+    };
+#pragma unroll
+    for (int c = 0; c < S - 1; ++c) issue();
+    float acc[R][GV_ROWS];
+    int cp_it = 0, cp_chunk = 0, cp_stage = 0, rows = 0, n0 = 0;
+    const int total = cnt * n_chunks;
+    for (int i = 0; i < total; ++i) {
+      issue();
+      gs_wait<S - 1>();                // this lane's requests for step i have landed
+      if (cp_chunk == 0) {
+#pragma unroll
+        for (int j = 0; j < R; ++j)
+#pragma unroll
+          for (int r = 0; r < GV_ROWS; ++r) acc[j][r] = 0.f;
+        rows = meta[cp_it * 8 + 2];
+        n0 = meta[cp_it * 8 + 3] * FEATS;
+      }
+      if (cp_chunk * GS_CHUNK + kl < a.K) {
+        const uint8_t* st = ring + (size_t)cp_stage * STAGE;
+        auto step = [&](auto nr_tag) {
+          constexpr int NR = decltype(nr_tag)::value;
+          float x[NR][8];
+#pragma unroll
+          for (int r = 0; r < NR; ++r) gs_unpack8(*(const uint4*)(st + (R + r) * 512), x[r]);
+#pragma unroll
+          for (int j = 0; j < R; ++j) {
+            if ((GATED ? n0 + (j >> 1) : n0 + j) >= a.N) continue;
+            float w[8];
+            gs_unpack8(*(const uint4*)(st + j * 512), w);
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[j][r] = fmaf(w[e], x[r][e], acc[j][r]);
+          }
+        };
+        if (rows <= 1) step(std::integral_constant<int, 1>{});
+        else if (rows == 2) step(std::integral_constant<int, 2>{});
+        else if (rows == 3) step(std::integral_constant<int, 3>{});
+        else step(std::integral_constant<int, GV_ROWS>{});
+      }
+      if (++cp_stage == S) cp_stage = 0;
+      if (++cp_chunk == n_chunks) {
+#pragma unroll
+        for (int j = 0; j < R; ++j)
+#pragma unroll
+          for (int r = 0; r < GV_ROWS; ++r) acc[j][r] = warp_sum(acc[j][r]);
+        if (lane == 0) {
+          const int group = meta[cp_it * 8], row0 = meta[cp_it * 8 + 1];
+#pragma unroll
+          for (int r = 0; r < GV_ROWS; ++r) {
+            if (r >= rows) continue;
+            const size_t crow = (size_t)(row0 + r) * a.ldc + (table ? 0 : (size_t)group * a.c_group_off);
+            if (GATED) {
+#pragma unroll
+              for (int f = 0; f < R / 2; ++f) {
+                const int n = n0 + f;
+                if (n >= a.N) continue;
+                const float g = fminf(acc[2 * f][r], a.limit);
+                const float u = fminf(fmaxf(acc[2 * f + 1][r], -a.limit), a.limit);
+                ((bf16*)a.C)[crow + n] = from_f<bf16>(g / (1.f + expf(-a.alpha * g)) * (u + 1.f));
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < R; ++j) {
+                const int n = n0 + j;
+                if (n >= a.N) continue;
+                if (a.epi == 1) ((float*)a.C)[crow + n] = acc[j][r];
+                else ((bf16*)a.C)[crow + n] = from_f<bf16>(grouped_act(acc[j][r], a.epi));
+              }
+            }
+          }
+        }
+        cp_chunk = 0; ++cp_it;
       }
     }
-  };
-  if (rows <= 1) walk(std::integral_constant<int, 1>{});
-  else if (rows == 2) walk(std::integral_constant<int, 2>{});
-  else walk(std::integral_constant<int, GV_ROWS>{});
-#pragma unroll
-  for (int j = 0; j < 8; ++j)
-#pragma unroll
-    for (int r = 0; r < GV_ROWS; ++r) acc[j][r] = warp_sum(acc[j][r]);
-  if (lane != 0) return;
-#pragma unroll
-  for (int r = 0; r < GV_ROWS; ++r) {
-    if (r >= rows) continue;
-    const size_t crow = (size_t)(row0 + r) * a.ldc + (a.tile_group != nullptr ? 0 : (size_t)group * a.c_group_off);
-    if (GATED) {
-#pragma unroll
-      for (int f = 0; f < 4; ++f) {
-        const int n = n0 + warp * 4 + f;
-        if (n >= a.N) continue;
-        const float g = fminf(acc[2 * f][r], a.limit);
-        const float u = fminf(fmaxf(acc[2 * f + 1][r], -a.limit), a.limit);
-        ((bf16*)a.C)[crow + n] = from_f<bf16>(g / (1.f + expf(-a.alpha * g)) * (u + 1.f));
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int n = n0 + warp * 8 + j;
-        if (n >= a.N) continue;
-        if (a.epi == 1) ((float*)a.C)[crow + n] = acc[j][r];
-        else ((bf16*)a.C)[crow + n] = from_f<bf16>(grouped_act(acc[j][r], a.epi));
-      }
-    }
+    gs_wait<0>();
+    __syncwarp();                      // the next 32 items overwrite the list
   }
 }
 
@@ -450,15 +485,36 @@ extern "C" int odi_grouped_gemm(const GroupedArgs* args, int max_tiles, int tm, 
       if (grid.z > 65535) return ODI_ERR_UNSUPPORTED;
     }
     if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
-    const size_t stream_smem = (size_t)GV_ROWS * a.K * 2 + (size_t)8 * GS_STAGES * 8 * 512;
-    if (dtype == 1 && stream_smem <= 200 * 1024 && getenv("ODI_GROUPED_GEMV") == nullptr) {
+    const char* form = getenv("ODI_GROUPED_GEMV");
+    if (dtype == 1 && (form == nullptr || strcmp(form, "registers") != 0)) {
       // bf16: the weights through a cp.async ring (ODI_GROUPED_GEMV=registers keeps the form above)
-#define ODI_GS(G) \
-      do { cudaError_t e = cudaFuncSetAttribute(grouped_gemv_stream_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stream_smem); \
+      static int sms = 0;
+      if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+          sms = 0;
+          return ODI_ERR_UNSUPPORTED;
+        }
+      }
+      const int per_feat = a.epi == 2 ? 2 : 1;            // weight rows a feature takes
+      const int row_tiles = a.tile_group != nullptr ? 0 : (a.M + GV_ROWS - 1) / GV_ROWS;
+      const long long tiles = a.tile_group != nullptr ? max_tiles : (long long)row_tiles * a.groups;
+      if (tiles * ((a.N + 1) / 2 + 1) > (1ll << 40)) return ODI_ERR_UNSUPPORTED;
+      // items of 8 weight rows ask in larger pieces; items of 4 spread a short list more evenly over the warps
+      const long long items8 = tiles * ((a.N * per_feat + 7) / 8);
+      const bool wide = form != nullptr ? strcmp(form, "walk8") == 0 : items8 >= 10ll * 8 * sms;
+      const int feats = (wide ? 8 : 4) / per_feat;
+      const long long items = tiles * ((a.N + feats - 1) / feats);
+      const int blocks = (int)std::min<long long>(sms, (items + 7) / 8);
+      const size_t walk_smem = (size_t)8 * 6 * (4 + GV_ROWS) * 512 + 8 * 32 * 8 * sizeof(int);   // equal for both shapes
+#define ODI_GW(G, R, S) \
+      do { cudaError_t e = cudaFuncSetAttribute(grouped_gemv_walk_kernel<G, R, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)walk_smem); \
            if (e != cudaSuccess) return (int)e; \
-           odi_rc = launch_pdl((grouped_gemv_stream_kernel<G>), grid, dim3(256), stream_smem, stream, a); } while (0)
-      if (a.epi == 2) ODI_GS(true); else ODI_GS(false);
-#undef ODI_GS
+           odi_rc = launch_pdl((grouped_gemv_walk_kernel<G, R, S>), dim3(blocks), dim3(256), walk_smem, stream, a, row_tiles); } while (0)
+      if (wide) { if (a.epi == 2) ODI_GW(true, 8, 4); else ODI_GW(false, 8, 4); }
+      else { if (a.epi == 2) ODI_GW(true, 4, 6); else ODI_GW(false, 4, 6); }
+#undef ODI_GW
       return launch_status();
     }
     const size_t smem = (size_t)GV_ROWS * a.K * sizeof(float);

@@ -307,6 +307,34 @@ def test_table_routed_experts_against_a_loop_over_tokens(dtype, tokens, experts,
     assert (acc.cpu().double() - want).abs().max() < (2e-5 if dtype == torch.float32 else 3e-2)
 
 
+@pytest.mark.parametrize("tokens,experts,top,K,F", [(7, 5, 3, 616, 1016),       # three chunks of k, the last one partial
+                                                    (6, 12, 2, 264, 4096),       # a list long enough for items of 8 weight rows
+                                                    (3, 4, 4, 136, 12800),       # the widest rows the form takes
+                                                    (1, 2, 1, 8, 8)])
+def test_single_token_expert_products_that_walk_item_lists(tokens, experts, top, K, F):
+    """bf16 products of a few rows per expert: every warp walks its own list of (tile, weight rows) items."""
+    g = torch.Generator().manual_seed(K)
+    ids = torch.stack([torch.randperm(experts, generator=g)[:top] for _ in range(tokens)]).int().cuda()
+    x = torch.randn(tokens, K, generator=g).bfloat16().cuda()
+    w_up = (torch.randn(experts, F, K, generator=g) / K ** 0.5).bfloat16().cuda()
+    w_down = (torch.randn(experts, K, F, generator=g) / F ** 0.5).bfloat16().cuda()
+    assert ops.grouped_few_rows_ok((K, F), torch.bfloat16)
+    routing = ops.RoutingTable(tokens, top, experts, "cuda", few_rows_ok=True)
+    counts = torch.zeros(experts, dtype=torch.int32, device="cuda")
+    ops.moe_group(ids, counts, routing)
+    act = torch.empty((tokens * top, F), dtype=torch.bfloat16, device="cuda")
+    ops.grouped_gemm_routed(x, w_up, act, routing, gather=True, epi=ops.GROUPED_GELU_ERF)
+    out = torch.empty((tokens * top, K), dtype=torch.float32, device="cuda")
+    ops.grouped_gemm_routed(act, w_down, out, routing, gather=False, epi=ops.GROUPED_STORE_F32)
+    perm = routing.perm[:tokens * top].long()          # sorted row i is pair perm[i] = token * top + choice
+    for i in range(tokens * top):
+        t, e = int(perm[i]) // top, int(ids.flatten()[perm[i]])
+        want = plain.gelu_erf(x[t].double() @ w_up[e].double().T)
+        assert ((act[i].double() - want).abs() <= 2e-2 + 1e-2 * want.abs()).all()
+        want = act[i].double() @ w_down[e].double().T
+        assert (out[i].double() - want).abs().max() < 1e-4
+
+
 # ----------------------------------------------------------------------------- whole models
 
 
